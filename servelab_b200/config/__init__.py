@@ -4,10 +4,12 @@ from .engine import CacheConfig, EngineConfig, SchedulerConfig
 from .daferax import DaferaxConfig
 from .dezelorn import DezelornConfig
 from .qwen2 import ConfigError, Qwen2Config
+from .zimupel import ZimupelConfig
 from .registry import (config_from_dict, load_config, model_spec_from_config,
                        register_architecture, registered_architectures,
                        resolve_architecture)
-from .specs import (AttentionSpec, BlockSpec, ConvTalkAttentionSpec, DynamicTanhSpec, GatedMLPSpec,
+from .specs import (AttentionSpec, BlockSpec, ConvTalkAttentionSpec, DecayAttentionSpec,
+                    DifferentialAttentionSpec, DynamicTanhSpec, GatedMLPSpec,
                     LatentAttentionSpec, LayerNormSpec, LayerRun, ModelSpec, NoPositionSpec,
                     NormedAttentionSpec, PairRotarySpec, PartSpec, RMSNormSpec, RotarySpec,
                     RoutedExpertsSpec)
@@ -15,13 +17,15 @@ from .specs import (AttentionSpec, BlockSpec, ConvTalkAttentionSpec, DynamicTanh
 register_architecture(Qwen2Config.architecture, Qwen2Config, model_type=Qwen2Config.model_type)
 register_architecture(DezelornConfig.architecture, DezelornConfig, model_type=DezelornConfig.model_type)
 register_architecture(DaferaxConfig.architecture, DaferaxConfig, model_type=DaferaxConfig.model_type)
+register_architecture(ZimupelConfig.architecture, ZimupelConfig, model_type=ZimupelConfig.model_type)
 
 __all__ = [
     "AttentionSpec", "BlockSpec", "CacheConfig", "ConfigError", "ConvTalkAttentionSpec",
-    "DaferaxConfig", "DezelornConfig", "DynamicTanhSpec", "EngineConfig",
+    "DaferaxConfig", "DecayAttentionSpec", "DezelornConfig", "DifferentialAttentionSpec", "DynamicTanhSpec",
+    "EngineConfig",
     "GatedMLPSpec", "LatentAttentionSpec", "LayerNormSpec", "LayerRun", "ModelSpec", "NoPositionSpec",
     "NormedAttentionSpec", "PairRotarySpec", "PartSpec",
-    "Qwen2Config", "RMSNormSpec", "RotarySpec", "RoutedExpertsSpec", "SchedulerConfig",
+    "Qwen2Config", "RMSNormSpec", "RotarySpec", "RoutedExpertsSpec", "SchedulerConfig", "ZimupelConfig",
     "config_from_dict", "load_config", "model_spec_from_config",
     "register_architecture", "registered_architectures", "resolve_architecture",
 ]

@@ -63,6 +63,7 @@ class RMSNormSpec(PartSpec):
     kind: str = "rmsnorm"
     dim: int = 0
     eps: float = 1e-6
+    weight_suffix: str = ".weight"         # the weight is <prefix><weight_suffix>
 
 
 @dataclass(frozen=True)
@@ -229,10 +230,77 @@ class LatentAttentionSpec(PartSpec):
     gate_name: str = "g"
 
 
+@dataclass(frozen=True)
+class DecayAttentionSpec(PartSpec):
+    """Linear attention with a fixed decay per head and a per-request state instead of cached
+    keys: S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t (no softmax, no denominator), S of
+    ``head_dim`` x ``value_dim`` float32 per head.  Around the recurrence, each a parameter:
+
+    ``qkv_activation``  None, or "silu" on the projected q, k and v;
+    ``position``        a ``RotarySpec`` (rotate-half over the first ``rotary_dim`` elements of every
+                        query and key head) or none;
+    ``key_scale``       a factor on the keys (after the rotation); None: 1;
+    ``out_norm``        "head": every head's result is divided by its root mean square;
+                        "row": the concatenated heads are RMS-normed together;
+                        with ``out_norm_weight`` a learned weight over the whole row multiplies;
+    ``gate_activation`` the result is multiplied by act(W_g x): "silu" or "sigmoid".
+    """
+    kind: str = "decay_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    decay: Tuple[float, ...] = ()
+    qkv_activation: Optional[str] = None
+    position: PartSpec = field(default_factory=NoPositionSpec)
+    key_scale: Optional[float] = None
+    out_norm: str = "head"
+    out_norm_weight: bool = False
+    out_norm_eps: float = 1e-6
+    gate_activation: str = "silu"
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    gate_name: str = "g"
+    o_name: str = "o"
+    out_norm_name: str = "norm"
+
+
+@dataclass(frozen=True)
+class DifferentialAttentionSpec(PartSpec):
+    """Grouped-query softmax attention with two maps a head: every query head and every kv head
+    carries two query / key vectors of ``head_dim`` elements ([head][map]), each map attends on
+    its own over the kv head's one set of values (``value_dim``), and a head's result is
+    o = a_1 - lambda a_2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + ``lambda_init`` (four
+    learned vectors of ``head_dim`` elements, one number a layer), divided by its root mean
+    square over the head (``norm_eps``, no weight) and multiplied by 1 - ``lambda_init``.  Biases
+    on q, k and v; positions do not enter the scores.  ``own_kv`` False: the layer has no key
+    and value projections and reads the cache that another layer fills."""
+    kind: str = "differential_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    scale: Optional[float] = None          # None => head_dim ** -0.5
+    lambda_init: float = 0.0
+    norm_eps: float = 1e-6
+    qkv_bias: bool = True
+    own_kv: bool = True
+    window: Optional[int] = None
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    o_name: str = "o"
+    bias_suffix: str = ".b"
+    lambda_names: Tuple[str, str, str, str] = ("lq1", "lk1", "lq2", "lk2")
+
+
 # -------------------------------------------------------------- feed-forward
 @dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
-    """down(act(gate(x)) * up(x)) with a dense (expert-free) gate/up/down."""
+    """down(act(gate(x)) * up(x)) with a dense (expert-free) gate/up/down; ``activation``
+    "silu" or "gelu_tanh"."""
     kind: str = "gated_mlp"
     hidden_size: int = 0
     intermediate_size: int = 0
@@ -251,7 +319,11 @@ class RoutedExpertsSpec(PartSpec):
     neighbours, a group scores as its best expert and only the ``keep_groups`` best groups'
     experts can be chosen; the chosen experts' outputs are weighted by their scores times
     ``route_scale`` (divided by the sum of the chosen scores first with ``renormalize``).
-    ``shared``: a dense gated feed-forward that every token also passes, added to the sum."""
+    ``shared``: a dense gated feed-forward that every token also passes, added to the sum.
+    ``score_fn`` "sigmoid": the scores are sigmoids of the logits.  ``correction_name``: a learned
+    offset per expert that is added to the scores for the choice (experts and groups) and not for
+    the weights.  ``group_best``: a group scores as the sum of its that many largest choice scores
+    (1: its best).  ``norm_eps``: added to the sum of the chosen scores with ``renormalize``."""
     kind: str = "routed_experts"
     hidden_size: int = 0
     num_experts: int = 0
@@ -262,6 +334,10 @@ class RoutedExpertsSpec(PartSpec):
     route_scale: float = 1.0
     renormalize: bool = False
     shared: Optional[PartSpec] = None
+    score_fn: str = "softmax"
+    correction_name: Optional[str] = None
+    group_best: int = 1
+    norm_eps: float = 0.0
     router_name: str = "router"
     expert_prefix: str = "e{}"             # expert j's tensors: <prefix>.e<j>.<gate|up|down>
     gate_name: str = "gate"
@@ -280,7 +356,11 @@ class BlockSpec(PartSpec):
     x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))); its ``feed_forward`` may be
     None (a layer that has a mixer only).
     ``result_norm`` norms only what a sublayer returns; the sublayers read the stream itself:
-    x += norm1(mixer(x)); x += norm2(ff(x)) (``mixer_post_norm``, ``ff_post_norm``)."""
+    x += norm1(mixer(x)); x += norm2(ff(x)) (``mixer_post_norm``, ``ff_post_norm``).
+    ``hyper_connections`` keeps ``streams`` copies of the residual: a sublayer reads
+    u = sum_s in[s] x_s, and x_t <- sum_s mix[s, t] x_s + out[t] f(norm(u)) for all streams at once
+    (tensors ``<layer>.<mixer_hyper_name>.{in,out,mix}`` and the same for the feed-forward, which
+    may be None)."""
     kind: str = "pre_norm"
     mixer: PartSpec = None
     feed_forward: PartSpec = None
@@ -295,6 +375,9 @@ class BlockSpec(PartSpec):
     feed_forward_name: str = "mlp"
     mixer_post_norm_name: str = "post_mixer_norm"
     ff_post_norm_name: str = "post_ff_norm"
+    streams: int = 1                       # (hyper_connections)
+    mixer_hyper_name: str = "hc1"
+    ff_hyper_name: str = "hc2"
 
 
 @dataclass(frozen=True)
@@ -337,5 +420,10 @@ class ModelSpec:
     ignored_suffixes: Tuple[str, ...] = ("rotary_emb.inv_freq",)
     # arithmetic around the layers that some architectures have; None: not applied
     embedding_scale: Optional[float] = None      # embedded tokens are multiplied by it
+    embedding_norm: Optional[PartSpec] = None    # an RMS norm on the embedded tokens
+    embedding_norm_prefix: str = "model.embed_norm"
+    # a number: the residual is kept as that many streams [tokens, streams, hidden], all equal to the
+    # embedding at the start and summed before the final norm (blocks of kind hyper_connections)
+    residual_streams: Optional[int] = None
     logit_scale: Optional[float] = None          # logits are multiplied by it ...
     logit_softcap: Optional[float] = None        # ... and then become cap * tanh(logits / cap)

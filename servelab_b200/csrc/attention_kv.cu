@@ -11,6 +11,12 @@
 // Optional epilogue: the row of head h is multiplied by sigmoid(gate[token][h]) (one number a
 // head).
 //
+// Several attention maps a head (`maps`, the differential form): every query head and every kv
+// head carries `maps` query / key vectors side by side ([head][map][Dk], key rows `ldk` apart),
+// each map is an attention of its own over the kv head's one set of values, and the results are
+// written map by map ([token][head][map][Dv], float32 if asked for), for the kernel that combines
+// them.  A block then owns (tile, kv head, map).
+//
 // Work unit: (tile of 32 flattened query rows rho = local_token * g + head_in_group, kv head).
 // Keys are visited in tiles of 32 aligned to absolute positions, in increasing order, with an
 // online softmax per row; the head dimension is walked in chunks of 64 through one shared
@@ -28,10 +34,10 @@
 
 SLB_DEFINE_STATUS_WORD(attention_kv_status_word, slb_attention_kv_status)
 
-template <typename T>
+template <typename T, typename TO>
 __global__ void __launch_bounds__(AK_THREADS) attention_kv_kernel(
-    const T* __restrict__ q, int ldq, const T* __restrict__ kc, const T* __restrict__ vc, int ldv,
-    T* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
+    const T* __restrict__ q, int ldq, const T* __restrict__ kc, int ldk, int maps, const T* __restrict__ vc, int ldv,
+    TO* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
     int H, int Hkv, int Dk, int Dv, int ps, int num_pages, float scale, int window,
@@ -45,7 +51,7 @@ __global__ void __launch_bounds__(AK_THREADS) attention_kv_kernel(
     __shared__ int page_of[AK_BN];
 
     const int tid = threadIdx.x;
-    const int kvh = blockIdx.y;
+    const int kvh = blockIdx.y / maps, map = blockIdx.y - kvh * maps;
     const int s = tile_seq[blockIdx.x];
     const int row0 = tile_row0[blockIdx.x];
     const int g = H / Hkv;
@@ -62,7 +68,7 @@ __global__ void __launch_bounds__(AK_THREADS) attention_kv_kernel(
         if (r < nrows) {
             const int rho = row0 + r;
             const int tl = rho / g, hg = rho - tl * g;
-            v = to_float(q[(size_t)(q0 + tl) * ldq + (size_t)(kvh * g + hg) * Dk + d]);
+            v = to_float(q[(size_t)(q0 + tl) * ldq + (size_t)((kvh * g + hg) * maps + map) * Dk + d]);
         }
         Qs[r * ldq_s + d] = v;
     }
@@ -108,7 +114,7 @@ __global__ void __launch_bounds__(AK_THREADS) attention_kv_kernel(
                 float kv = 0.f;
                 if (page >= 0 && d0 + d < Dk) {
                     const size_t slot = ((size_t)page * Hkv + kvh) * ps + (k0 + kr) % ps;
-                    kv = to_float(kc[slot * Dk + d0 + d]);
+                    kv = to_float(kc[slot * ldk + map * Dk + d0 + d]);
                 }
                 Cs[kr * (AK_DC + 1) + d] = kv;
             }
@@ -180,42 +186,42 @@ __global__ void __launch_bounds__(AK_THREADS) attention_kv_kernel(
     if (row_valid) {
         const int rho = row0 + r;
         const int tl = rho / g, hg = rho - tl * g;
-        const int head = kvh * g + hg;
+        const int head = (kvh * g + hg) * maps + map;
         float inv = l > 0.f ? 1.0f / l : 0.f;
         if (gate != nullptr) {
             const float z = to_float(gate[(size_t)(q0 + tl) * ldg + head]);
             inv *= 1.0f / (1.0f + expf(-z));
         }
-        T* o = out + (size_t)(q0 + tl) * ldo + (size_t)head * Dv;
+        TO* o = out + (size_t)(q0 + tl) * ldo + (size_t)head * Dv;
 #pragma unroll
         for (int vci = 0; vci < AK_MAX_DV / AK_DC; ++vci)
 #pragma unroll
             for (int j = 0; j < AK_DC / 8; ++j) {
                 const int c = vci * AK_DC + c0 + 8 * j;
-                if (vci < nvc && c < Dv) o[c] = from_float<T>(acc[vci][j] * inv);
+                if (vci < nvc && c < Dv) o[c] = from_float<TO>(acc[vci][j] * inv);
             }
     }
 }
 
-template <typename T>
-static int launch_attention_kv(const T* q, int ldq, const T* kc, const T* vc, int ldv, T* out, int ldo,
+template <typename T, typename TO>
+static int launch_attention_kv(const T* q, int ldq, const T* kc, int ldk, int maps, const T* vc, int ldv, TO* out, int ldo,
                                const int* block_table, int max_pages, const int* cu_q,
                                const int* ctx_len, const int* tile_seq, const int* tile_row0,
                                int num_tiles, int H, int Hkv, int Dk, int Dv, int ps, int num_pages,
                                float scale, int window, const T* gate, int ldg, cudaStream_t st) {
     if (num_tiles <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || Dk <= 0 || Dv <= 0 || ps <= 0 || max_pages <= 0 ||
-        num_pages <= 0 || ldv < Dv)
+        num_pages <= 0 || ldv < Dv || maps <= 0 || ldk < maps * Dk)
         return SLB_ERR_BAD_ARG;
-    if (Dk > AK_MAX_DK || Dv > AK_MAX_DV || Hkv > 65535) return SLB_ERR_TOO_LARGE;
+    if (Dk > AK_MAX_DK || Dv > AK_MAX_DV || Hkv * maps > 65535) return SLB_ERR_TOO_LARGE;
     const size_t smem = ((size_t)AK_BM * (Dk + 1) + AK_BN * (AK_DC + 1) + AK_BM * (AK_BN + 1)) * sizeof(float);
     constexpr size_t SMEM_MAX =
         ((size_t)AK_BM * (AK_MAX_DK + 1) + AK_BN * (AK_DC + 1) + AK_BM * (AK_BN + 1)) * sizeof(float);
     static unsigned long long configured = 0;
-    const int rc = slb_configure(&configured, attention_kv_kernel<T>, SMEM_MAX);
+    const int rc = slb_configure(&configured, attention_kv_kernel<T, TO>, SMEM_MAX);
     if (rc != 0) return rc;
-    return slb_launch(attention_kv_kernel<T>, dim3(num_tiles, Hkv), dim3(AK_THREADS), smem, st, q, ldq,
-                      kc, vc, ldv, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq, tile_row0,
+    return slb_launch(attention_kv_kernel<T, TO>, dim3(num_tiles, Hkv * maps), dim3(AK_THREADS), smem, st, q, ldq,
+                      kc, ldk, maps, vc, ldv, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq, tile_row0,
                       H, Hkv, Dk, Dv, ps, num_pages, scale, window, gate, ldg);
 }
 
@@ -226,7 +232,7 @@ int slb_attention_kv_f32(const float* q, int ldq, const float* kc, const float* 
                          const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
                          int H, int Hkv, int Dk, int Dv, int ps, int num_pages, float scale, int window,
                          const float* gate, int ldg, cudaStream_t st) {
-    return launch_attention_kv<float>(q, ldq, kc, vc, ldv, out, ldo, block_table, max_pages, cu_q,
+    return launch_attention_kv<float, float>(q, ldq, kc, Dk, 1, vc, ldv, out, ldo, block_table, max_pages, cu_q,
                                       ctx_len, tile_seq, tile_row0, num_tiles, H, Hkv, Dk, Dv, ps,
                                       num_pages, scale, window, gate, ldg, st);
 }
@@ -235,8 +241,27 @@ int slb_attention_kv_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc
                           const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
                           int H, int Hkv, int Dk, int Dv, int ps, int num_pages, float scale, int window,
                           const bf16* gate, int ldg, cudaStream_t st) {
-    return launch_attention_kv<bf16>(q, ldq, kc, vc, ldv, out, ldo, block_table, max_pages, cu_q,
+    return launch_attention_kv<bf16, bf16>(q, ldq, kc, Dk, 1, vc, ldv, out, ldo, block_table, max_pages, cu_q,
                                      ctx_len, tile_seq, tile_row0, num_tiles, H, Hkv, Dk, Dv, ps,
                                      num_pages, scale, window, gate, ldg, st);
+}
+// several maps a head (see the top of the file); the results are float32 in both forms
+int slb_attention_kv_maps_f32(const float* q, int ldq, const float* kc, int ldk, int maps, const float* vc, int ldv,
+                              float* out, int ldo, const int* block_table, int max_pages, const int* cu_q,
+                              const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
+                              int H, int Hkv, int Dk, int Dv, int ps, int num_pages, float scale, int window,
+                              cudaStream_t st) {
+    return launch_attention_kv<float, float>(q, ldq, kc, ldk, maps, vc, ldv, out, ldo, block_table, max_pages, cu_q,
+                                             ctx_len, tile_seq, tile_row0, num_tiles, H, Hkv, Dk, Dv, ps,
+                                             num_pages, scale, window, nullptr, 0, st);
+}
+int slb_attention_kv_maps_bf16(const bf16* q, int ldq, const bf16* kc, int ldk, int maps, const bf16* vc, int ldv,
+                               float* out, int ldo, const int* block_table, int max_pages, const int* cu_q,
+                               const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
+                               int H, int Hkv, int Dk, int Dv, int ps, int num_pages, float scale, int window,
+                               cudaStream_t st) {
+    return launch_attention_kv<bf16, float>(q, ldq, kc, ldk, maps, vc, ldv, out, ldo, block_table, max_pages, cu_q,
+                                            ctx_len, tile_seq, tile_row0, num_tiles, H, Hkv, Dk, Dv, ps,
+                                            num_pages, scale, window, nullptr, 0, st);
 }
 }

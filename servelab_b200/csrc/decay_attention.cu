@@ -1,0 +1,165 @@
+// Linear attention with a fixed decay per head, as a recurrence over a per-request state:
+//
+//     S_t = decay_h S_{t-1} + k_t v_t^T        (S: D x Dv per head, float32, kept in a state slot)
+//     o_t = S_t^T q_t
+//
+// q, k and v are columns of one projected row per token.  Before they enter the recurrence the
+// kernel applies, each optional: an activation (SiLU) on q, k and v; a rotation of the first
+// `rot_dims` elements of every query and key head (element i with element i + rot_dims / 2, angle
+// position * freq[i]); a factor on the keys.  Everything after the load is float32: activations,
+// angles, the state, the products and the sums.  No softmax, no denominator.
+//
+// Plain form (this kernel): a block owns (request, head, 32 value columns); thread (part, column)
+// keeps the state elements S[d][column] for d = part, part + 8, ... in registers, so a token costs
+// D / 8 multiply-adds for the state and as many for the output, and the eight parts of an output
+// are added through shared memory in a fixed order.  Tokens of the request's portion are taken in
+// order, eight at a time (their prepared q, k, v rows staged in shared memory).  The state is
+// read from the request's slot at the start and written back at the end, so a request can be cut
+// anywhere: the result of a token is bit-identical however the prompt is cut and whatever else is
+// in the batch.  Steps of single tokens run the same kernel: then it is one read and one write of
+// the state.
+#include "common.cuh"
+
+#define DA_EV 32
+#define DA_PARTS 8
+#define DA_TT 8
+#define DA_MAX_D 256
+#define DA_R (DA_MAX_D / DA_PARTS)
+
+struct DecayAttnArgs {
+    const void* proj; int ld;
+    int q_off, k_off, v_off;
+    int H, D, Dv;
+    int act;                       // 0: none; 1: SiLU on q, k and v
+    const float* freq; int rot_dims;
+    float k_scale;
+    const float* decay;            // [H]
+    const int* positions; const int* cu_q; const int* state_slots;
+    float* state; int num_slots;   // [num_slots][H][D][Dv]
+    float* out; int ldo;           // [T][H * Dv] float32
+};
+
+__device__ __forceinline__ float da_silu(float z) { return z / (1.0f + expf(-z)); }
+
+// element d of a query or key head of token `row` (a pointer to the head's first element)
+template <typename T>
+__device__ __forceinline__ float da_prepared(const T* head, int d, int pos, const DecayAttnArgs& a) {
+    float x = to_float(head[d]);
+    if (a.act == 1) x = da_silu(x);
+    if (d < a.rot_dims) {
+        const int half = a.rot_dims >> 1;
+        const int i = d < half ? d : d - half;
+        float other = to_float(head[d < half ? d + half : d - half]);
+        if (a.act == 1) other = da_silu(other);
+        float sn, cs;
+        sincosf((float)pos * a.freq[i], &sn, &cs);
+        x = d < half ? x * cs - other * sn : x * cs + other * sn;
+    }
+    return x;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(DA_EV * DA_PARTS) decay_attention_kernel(const DecayAttnArgs a) {
+    extern __shared__ float da_smem[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int s = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * DA_EV;
+    const int q0 = a.cu_q[s];
+    const int qlen = a.cu_q[s + 1] - q0;
+    if (qlen <= 0) return;
+    const int slot = a.state_slots[s];
+    if (slot < 0 || slot >= a.num_slots) return;
+    const int D = a.D, Dv = a.Dv;
+    float* qs = da_smem;                         // [DA_TT][D]
+    float* ks = qs + DA_TT * D;                  // [DA_TT][D]
+    float* vs = ks + DA_TT * D;                  // [DA_TT][DA_EV]
+    float* part = vs + DA_TT * DA_EV;            // [DA_TT][DA_PARTS][DA_EV]
+    const int tid = threadIdx.x, p = tid >> 5, e = tid & 31;
+    const int col = e0 + e;
+    const bool live = col < Dv;
+    const float dec = a.decay[h];
+    float* srow = a.state + ((size_t)slot * a.H + h) * (size_t)D * Dv;
+
+    float st[DA_R];
+#pragma unroll
+    for (int i = 0; i < DA_R; ++i) {
+        const int d = i * DA_PARTS + p;
+        st[i] = (live && d < D) ? srow[(size_t)d * Dv + col] : 0.f;
+    }
+    const T* proj = reinterpret_cast<const T*>(a.proj);
+    for (int t0 = 0; t0 < qlen; t0 += DA_TT) {
+        const int n = min(DA_TT, qlen - t0);
+        for (int idx = tid; idx < n * D; idx += DA_EV * DA_PARTS) {
+            const int j = idx / D, d = idx - j * D;
+            const T* row = proj + (size_t)(q0 + t0 + j) * a.ld;
+            const int pos = a.positions[q0 + t0 + j];
+            qs[j * D + d] = da_prepared(row + a.q_off + h * D, d, pos, a);
+            ks[j * D + d] = da_prepared(row + a.k_off + h * D, d, pos, a) * a.k_scale;
+        }
+        for (int idx = tid; idx < n * DA_EV; idx += DA_EV * DA_PARTS) {
+            const int j = idx / DA_EV, c = e0 + (idx - j * DA_EV);
+            float v = 0.f;
+            if (c < Dv) {
+                v = to_float(proj[(size_t)(q0 + t0 + j) * a.ld + a.v_off + h * Dv + c]);
+                if (a.act == 1) v = da_silu(v);
+            }
+            vs[idx] = v;
+        }
+        __syncthreads();
+        for (int j = 0; j < n; ++j) {
+            const float v = vs[j * DA_EV + e];
+            const float* qj = qs + j * D;
+            const float* kj = ks + j * D;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < DA_R; ++i) {
+                const int d = i * DA_PARTS + p;
+                if (d < D) {
+                    st[i] = fmaf(dec, st[i], kj[d] * v);
+                    acc = fmaf(st[i], qj[d], acc);
+                }
+            }
+            part[(j * DA_PARTS + p) * DA_EV + e] = acc;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < n * DA_EV; idx += DA_EV * DA_PARTS) {
+            const int j = idx / DA_EV, c = idx - j * DA_EV;
+            if (e0 + c < Dv) {
+                float o = 0.f;
+#pragma unroll
+                for (int pp = 0; pp < DA_PARTS; ++pp) o += part[(j * DA_PARTS + pp) * DA_EV + c];
+                a.out[(size_t)(q0 + t0 + j) * a.ldo + h * Dv + e0 + c] = o;
+            }
+        }
+        // (the next tile's loads touch qs, ks and vs, which every thread has finished reading
+        // before the second barrier; `part` is written again only after the next first barrier)
+    }
+#pragma unroll
+    for (int i = 0; i < DA_R; ++i) {
+        const int d = i * DA_PARTS + p;
+        if (live && d < D) srow[(size_t)d * Dv + col] = st[i];
+    }
+}
+
+template <typename T>
+static int launch_decay_attention(const DecayAttnArgs* a, int num_seqs, cudaStream_t st) {
+    if (num_seqs <= 0) return 0;
+    if (a->H <= 0 || a->D <= 0 || a->Dv <= 0 || a->num_slots <= 0 || (a->rot_dims & 1) || a->rot_dims < 0 ||
+        a->rot_dims > a->D || (a->rot_dims > 0 && a->freq == nullptr) || a->act < 0 || a->act > 1)
+        return SLB_ERR_BAD_ARG;
+    if (a->D > DA_MAX_D || a->H > 65535) return SLB_ERR_TOO_LARGE;
+    const int vz = (a->Dv + DA_EV - 1) / DA_EV;
+    if (vz > 65535) return SLB_ERR_TOO_LARGE;
+    const size_t smem = ((size_t)2 * DA_TT * a->D + DA_TT * DA_EV + DA_TT * DA_PARTS * DA_EV) * sizeof(float);
+    return slb_launch(decay_attention_kernel<T>, dim3(num_seqs, a->H, vz), dim3(DA_EV * DA_PARTS), smem, st, *a);
+}
+
+extern "C" {
+int slb_decay_attention_max_dim() { return DA_MAX_D; }
+int slb_decay_attention_f32(const DecayAttnArgs* a, int num_seqs, cudaStream_t st) {
+    return launch_decay_attention<float>(a, num_seqs, st);
+}
+int slb_decay_attention_bf16(const DecayAttnArgs* a, int num_seqs, cudaStream_t st) {
+    return launch_decay_attention<bf16>(a, num_seqs, st);
+}
+}

@@ -330,7 +330,19 @@ __device__ __forceinline__ float silu_mul_fast(float g, float u) {
     return g * __frcp_rn(1.0f + __expf(-g)) * u;
 }
 
-template <typename T, int V>
+// the tanh form of GELU: 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gelu_tanh_mul(float g, float u) {
+    return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+}
+template <int ACT> __device__ __forceinline__ float act_mul(float g, float u) {
+    return ACT == 1 ? gelu_tanh_mul(g, u) : silu_mul(g, u);
+}
+template <int ACT> __device__ __forceinline__ float act_mul_fast(float g, float u) {
+    return ACT == 1 ? gelu_tanh_mul(g, u) : silu_mul_fast(g, u);
+}
+
+// ACT 0: SiLU; 1: GELU (tanh form)
+template <typename T, int V, int ACT>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                               int ld_gu, int ld_out, int block) {
     pdl_launch_dependents();
@@ -353,15 +365,15 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-            r2[e] = __floats2bfloat162_rn(silu_mul_fast(g.x, u.x), silu_mul_fast(g.y, u.y));
+            r2[e] = __floats2bfloat162_rn(act_mul_fast<ACT>(g.x, u.x), act_mul_fast<ACT>(g.y, u.y));
         }
         *reinterpret_cast<uint4*>(o + i) = res;
     } else if constexpr (V == 4) {
         const float4 g = load4(row + gi), u = load4(row + ui);
-        store4(o + i, make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z),
-                                  silu_mul(g.w, u.w)));
+        store4(o + i, make_float4(act_mul<ACT>(g.x, u.x), act_mul<ACT>(g.y, u.y), act_mul<ACT>(g.z, u.z),
+                                  act_mul<ACT>(g.w, u.w)));
     } else {
-        o[i] = from_float<T>(silu_mul(to_float(row[gi]), to_float(row[ui])));
+        o[i] = from_float<T>(act_mul<ACT>(to_float(row[gi]), to_float(row[ui])));
     }
 }
 
@@ -401,7 +413,7 @@ static int launch_add_rmsnorm(float* resid, const TD* delta, const float* parts,
 #undef SLB_NORM_LAUNCH
 }
 
-template <typename T>
+template <typename T, int ACT>
 static int launch_swiglu(const T* gu, T* out, int T_, int inter, int ld_gu, int ld_out, int block,
                          cudaStream_t st) {
     if (T_ <= 0) return 0;
@@ -409,13 +421,13 @@ static int launch_swiglu(const T* gu, T* out, int T_, int inter, int ld_gu, int 
     if constexpr (sizeof(T) == 2) {
         if (inter % 8 == 0 && block % 8 == 0 && ld_gu % 8 == 0 && ld_out % 8 == 0 &&
             ((uintptr_t)gu | (uintptr_t)out) % 16 == 0)
-            return slb_launch(swiglu_kernel<T, 8>, dim3((inter / 8 + 255) / 256, T_), dim3(256), 0, st,
+            return slb_launch(swiglu_kernel<T, 8, ACT>, dim3((inter / 8 + 255) / 256, T_), dim3(256), 0, st,
                               gu, out, inter, ld_gu, ld_out, block);
     }
     if (inter % 4 == 0 && block % 4 == 0 && ld_gu % 4 == 0 && ld_out % 4 == 0)
-        return slb_launch(swiglu_kernel<T, 4>, dim3((inter / 4 + 255) / 256, T_), dim3(256), 0, st,
+        return slb_launch(swiglu_kernel<T, 4, ACT>, dim3((inter / 4 + 255) / 256, T_), dim3(256), 0, st,
                           gu, out, inter, ld_gu, ld_out, block);
-    return slb_launch(swiglu_kernel<T, 1>, dim3((inter + 255) / 256, T_), dim3(256), 0, st, gu,
+    return slb_launch(swiglu_kernel<T, 1, ACT>, dim3((inter + 255) / 256, T_), dim3(256), 0, st, gu,
                       out, inter, ld_gu, ld_out, block);
 }
 
@@ -485,11 +497,24 @@ int slb_add_rmsnorm_parts_bf16(float* resid, const float* parts, int nparts, lon
 // block: 0, or the run length in which gates and ups alternate in a row of gu
 int slb_swiglu_f32(const float* gu, float* out, int T, int inter, int ld_gu, int ld_out, int block,
                    cudaStream_t st) {
-    return launch_swiglu<float>(gu, out, T, inter, ld_gu, ld_out, block, st);
+    return launch_swiglu<float, 0>(gu, out, T, inter, ld_gu, ld_out, block, st);
 }
 int slb_swiglu_bf16(const bf16* gu, bf16* out, int T, int inter, int ld_gu, int ld_out, int block,
                     cudaStream_t st) {
-    return launch_swiglu<bf16>(gu, out, T, inter, ld_gu, ld_out, block, st);
+    return launch_swiglu<bf16, 0>(gu, out, T, inter, ld_gu, ld_out, block, st);
+}
+// the same with the activation as an argument: 0 SiLU, 1 GELU (tanh form)
+int slb_gated_act_f32(const float* gu, float* out, int T, int inter, int ld_gu, int ld_out, int block, int act,
+                      cudaStream_t st) {
+    if (act == 0) return launch_swiglu<float, 0>(gu, out, T, inter, ld_gu, ld_out, block, st);
+    if (act == 1) return launch_swiglu<float, 1>(gu, out, T, inter, ld_gu, ld_out, block, st);
+    return SLB_ERR_BAD_ARG;
+}
+int slb_gated_act_bf16(const bf16* gu, bf16* out, int T, int inter, int ld_gu, int ld_out, int block, int act,
+                       cudaStream_t st) {
+    if (act == 0) return launch_swiglu<bf16, 0>(gu, out, T, inter, ld_gu, ld_out, block, st);
+    if (act == 1) return launch_swiglu<bf16, 1>(gu, out, T, inter, ld_gu, ld_out, block, st);
+    return SLB_ERR_BAD_ARG;
 }
 
 }  // extern "C"

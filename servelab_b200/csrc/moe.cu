@@ -6,6 +6,9 @@
 //                      the `keep` best groups can be chosen; the `top` largest scores among those
 //                      are the choice (ties: the lower index); weight = score * route_scale
 //                      (optionally divided by the sum of the chosen scores).
+//   slb_moe_route_scored  the same with sigmoid scores, an offset per expert that enters the choice
+//                      only, groups that score as the sum of their best few, and a constant in the
+//                      denominator of the renormalised weights, each an argument.
 //   slb_moe_plan       (token, choice) pairs sorted by expert: counts, offsets, the list, and the
 //                      row tiles of the products (tile -> expert, first row), of a length that
 //                      depends only on the number of pairs and experts (a fixed grid).
@@ -37,80 +40,120 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
+// One warp a token.  `score_fn` 0: scores = softmax(logits); 1: scores = sigmoid(logits).  The
+// choice runs on choice scores c = score (+ correction[e], a learned offset that enters the choice
+// only); a group's score is the sum of its `group_best` largest choice scores (1: its maximum);
+// experts outside the `keep` best groups count as minus infinity (choice scores may be negative);
+// the weights are the chosen experts' scores without the offset, divided by their sum + `norm_eps`
+// with `renormalize`, times `route_scale`.  Ties: the lower index.
 __global__ void __launch_bounds__(128) moe_route_kernel(
     const float* __restrict__ logits, int ldl, int T, int E, int groups, int keep, int top,
-    float route_scale, int renormalize, int* __restrict__ ids, float* __restrict__ weights) {
+    float route_scale, int renormalize, int score_fn, const float* __restrict__ correction, int group_best,
+    float norm_eps, int* __restrict__ ids, float* __restrict__ weights) {
     extern __shared__ float route_smem[];
     pdl_wait();
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
     if (t >= T) return;
-    float* s = route_smem + (size_t)warp * (E + groups);      // scores, then the groups' scores
-    float* gs = s + E;
+    float* s = route_smem + (size_t)warp * (2 * E + 2 * groups);   // scores, choice scores,
+    float* c = s + E;                                                // the groups' scores and marks
+    float* gs = c + E;
+    float* gmark = gs + groups;
     const float* z = logits + (size_t)t * ldl;
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) {
-        const float p = expf(z[e] - mx);
-        s[e] = p;
-        sum += p;
+    if (score_fn == 0) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float p = expf(z[e] - mx);
+            s[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < E; e += 32) s[e] *= inv;
+    } else {
+        for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-z[e]));
     }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < E; e += 32) s[e] *= inv;
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) c[e] = correction != nullptr ? s[e] + correction[e] : s[e];
     __syncwarp();
     const int per = E / groups;
     if (groups > 1) {
         for (int g = lane; g < groups; g += 32) {
-            float b = -1.f;
-            for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, s[e]);
-            gs[g] = b;
+            // the sum of the group's `group_best` largest choice scores (all of them if it has fewer)
+            float total = 0.f;
+            int prev_i = -1;
+            float prev_v = INFINITY;
+            const int take = group_best < per ? group_best : per;
+            for (int r = 0; r < take; ++r) {
+                float b = -INFINITY;
+                int bi = -1;
+                for (int e = g * per; e < (g + 1) * per; ++e) {
+                    const float v = c[e];
+                    const bool after = v < prev_v || (v == prev_v && e > prev_i);   // not yet taken
+                    if (after && (bi < 0 || v > b)) {
+                        b = v;
+                        bi = e;
+                    }
+                }
+                if (bi < 0) break;
+                total += b;
+                prev_v = b;
+                prev_i = bi;
+            }
+            gs[g] = total;
+            gmark[g] = 0.f;
         }
         __syncwarp();
-        // the `keep` best groups get the mark 2 (a score is at most 1)
         for (int round = 0; round < keep; ++round) {
-            float bv = -1.f;
+            float bv = -INFINITY;
             int bi = 0x7fffffff;
             for (int g = lane; g < groups; g += 32)
-                if (gs[g] <= 1.5f && (gs[g] > bv || (gs[g] == bv && g < bi))) {
+                if (gmark[g] == 0.f && (gs[g] > bv || (gs[g] == bv && g < bi) || bi == 0x7fffffff) && gs[g] == gs[g]) {
                     bv = gs[g];
                     bi = g;
                 }
             warp_argmax(bv, bi);
-            if (lane == 0 && bi < groups) gs[bi] = 2.f;      // (no group found: logits that are no numbers)
+            if (lane == 0 && bi < groups) gmark[bi] = 1.f;   // (no group found: logits that are no numbers)
             __syncwarp();
         }
+        for (int e = lane; e < E; e += 32)
+            if (gmark[e / per] == 0.f) c[e] = -INFINITY;
+        __syncwarp();
     }
     float chosen_sum = 0.f;
     for (int round = 0; round < top; ++round) {
-        float bv = -1.f;
+        float bv = -INFINITY;
         int bi = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
-            const bool ok = groups <= 1 || gs[e / per] > 1.5f;
-            if (ok && s[e] >= 0.f && (s[e] > bv || (s[e] == bv && e < bi))) {
-                bv = s[e];
+            const float v = c[e];
+            if (v > -INFINITY && (v > bv || (v == bv && e < bi) || bi == 0x7fffffff)) {
+                bv = v;
                 bi = e;
             }
         }
         warp_argmax(bv, bi);
+        float w = 0.f;
         if (bi >= E) {                                     // nothing left to choose (logits that are no
             bi = 0;                                        // numbers, as the rows of a padded step may
-            bv = 0.f;                                      // hold): expert 0 with weight 0
+        } else {                                           // hold): expert 0 with weight 0
+            w = s[bi];
         }
+        __syncwarp();
         if (lane == 0) {
             ids[(size_t)t * top + round] = bi;
-            weights[(size_t)t * top + round] = bv;
-            if (bv > 0.f) s[bi] = -1.f;                    // taken
+            weights[(size_t)t * top + round] = w;
+            if (w == w && c[bi] > -INFINITY) c[bi] = -INFINITY;      // taken
         }
-        chosen_sum += bv;
+        chosen_sum += w;
         __syncwarp();
     }
     if (lane < top) {
         float w = weights[(size_t)t * top + lane];
-        if (renormalize) w /= chosen_sum;
+        if (renormalize) w /= (chosen_sum + norm_eps);
         weights[(size_t)t * top + lane] = w * route_scale;
     }
 }
@@ -481,16 +524,31 @@ int slb_moe_down_mma_bf16(const bf16* act, int lda, const bf16* w_down, int ldw,
     return launch_moe_mma<1>(act, lda, w_down, (long long)N * ldw, ldw, y, ldy, plan, E, P, top, N, I, st);
 }
 int slb_moe_tile_rows() { return MOE_BM; }
-int slb_moe_route(const float* logits, int ldl, int T, int E, int groups, int keep, int top,
-                  float route_scale, int renormalize, int* ids, float* weights, cudaStream_t st) {
+static int launch_moe_route(const float* logits, int ldl, int T, int E, int groups, int keep, int top,
+                            float route_scale, int renormalize, int score_fn, const float* correction,
+                            int group_best, float norm_eps, int* ids, float* weights, cudaStream_t st) {
     if (T <= 0) return 0;
     if (E <= 0 || groups <= 0 || E % groups != 0 || keep <= 0 || keep > groups || top <= 0 ||
-        top > (E / groups) * keep)
+        top > (E / groups) * keep || score_fn < 0 || score_fn > 1 || group_best < 1)
         return SLB_ERR_BAD_ARG;
     if (E > MOE_MAX_EXPERTS || top > MOE_MAX_TOP) return SLB_ERR_TOO_LARGE;
-    const size_t smem = (size_t)4 * (E + groups) * sizeof(float);
+    const size_t smem = (size_t)4 * (2 * E + 2 * groups) * sizeof(float);
     return slb_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), smem, st, logits, ldl, T, E, groups,
-                      keep, top, route_scale, renormalize, ids, weights);
+                      keep, top, route_scale, renormalize, score_fn, correction, group_best, norm_eps, ids,
+                      weights);
+}
+// the softmax router whose groups score as their best expert
+int slb_moe_route(const float* logits, int ldl, int T, int E, int groups, int keep, int top,
+                  float route_scale, int renormalize, int* ids, float* weights, cudaStream_t st) {
+    return launch_moe_route(logits, ldl, T, E, groups, keep, top, route_scale, renormalize, 0, nullptr, 1, 0.f,
+                            ids, weights, st);
+}
+// every choice of the route kernel as an argument
+int slb_moe_route_scored(const float* logits, int ldl, int T, int E, int groups, int keep, int top,
+                         float route_scale, int renormalize, int score_fn, const float* correction,
+                         int group_best, float norm_eps, int* ids, float* weights, cudaStream_t st) {
+    return launch_moe_route(logits, ldl, T, E, groups, keep, top, route_scale, renormalize, score_fn, correction,
+                            group_best, norm_eps, ids, weights, st);
 }
 int slb_router_logits_f32(const float* x, int ldx, const float* w, int ldw, float* logits, int ldl, int M,
                           int E, int K, cudaStream_t st) {

@@ -31,6 +31,8 @@ def declare_tensors(spec: ModelSpec) -> List[TensorDecl]:
     out = [TensorDecl(spec.embed_name, (spec.vocab_size, spec.hidden_size), MATRIX)]
     out += part_class(POSITIONS, spec.embedding_position).declare(spec.embedding_position,
                                                                   spec.embedding_position_prefix)
+    if spec.embedding_norm is not None:
+        out += part_class(NORMS, spec.embedding_norm).declare(spec.embedding_norm, spec.embedding_norm_prefix)
     for i, block in enumerate(spec.layers):
         out += part_class(BLOCKS, block).declare(block, spec.layer_prefix.format(i))
     out += part_class(NORMS, spec.final_norm).declare(spec.final_norm, spec.final_norm_prefix)
@@ -54,6 +56,15 @@ class CausalLM:
         self.final_norm = build_part(NORMS, spec.final_norm, spec.final_norm_prefix, env)
         self.embedding_position = build_part(POSITIONS, spec.embedding_position,
                                              spec.embedding_position_prefix, env)
+        self.embedding_norm = None
+        if spec.embedding_norm is not None:
+            if spec.embedding_norm.kind != "rmsnorm":
+                raise ValueError("the norm on the embedded tokens is an RMS norm")
+            self.embedding_norm = build_part(NORMS, spec.embedding_norm, spec.embedding_norm_prefix, env)
+        if spec.residual_streams is not None and not all(b.kind == "hyper_connections" and
+                                                         b.streams == spec.residual_streams for b in spec.layers):
+            raise ValueError("a residual kept as several streams needs blocks of kind hyper_connections "
+                             "with that many streams")
         self.embed_tokens: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
 
@@ -72,6 +83,8 @@ class CausalLM:
                             ignored_suffixes=self.spec.ignored_suffixes, optional=optional)
         self.embed_tokens = store.get(self.spec.embed_name)
         self.embedding_position.load(store)
+        if self.embedding_norm is not None:
+            self.embedding_norm.load(store)
         for b in self.blocks:
             b.load(store)
         self.final_norm.load(store)
@@ -103,9 +116,19 @@ class CausalLM:
         """Run the step's tokens; ``caches`` maps a run's index to its cache.
         Returns logits [wanted rows, vocab] float32."""
         T = ctx.num_tokens
-        resid = torch.empty((T, self.spec.hidden_size), dtype=torch.float32, device=self.env.device)
-        K.embedding(ctx.token_ids, self.embed_tokens, resid,
-                    1.0 if self.spec.embedding_scale is None else self.spec.embedding_scale)
+        n = self.spec.residual_streams
+        shape = (T, self.spec.hidden_size) if n is None else (T, n, self.spec.hidden_size)
+        resid = torch.empty(shape, dtype=torch.float32, device=self.env.device)
+        if self.embedding_norm is None and n is None:
+            K.embedding(ctx.token_ids, self.embed_tokens, resid,
+                        1.0 if self.spec.embedding_scale is None else self.spec.embedding_scale)
+        else:
+            # gather, RMS norm and the copies for every stream in one launch
+            if self.spec.embedding_scale is not None:
+                raise ValueError("an embedding scale together with an embedding norm or streams is not built")
+            norm = self.embedding_norm
+            K.embed_norm_streams(ctx.token_ids, self.embed_tokens, None if norm is None else norm.weight,
+                                 0.0 if norm is None else norm.spec.eps, resid)
         self.embedding_position.apply_to_embedding(ctx, resid)
         delta = None
         for i, run in enumerate(self.spec.run_order):

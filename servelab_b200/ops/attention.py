@@ -151,3 +151,15 @@ def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk,
         return
     K.attention_kv(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk, Dv, page_size, scale,
                    window, head_gate)
+
+
+# ------------------------------------------------- several attention maps a head
+def prepare_maps_attention(key_dim: int, value_dim: int, dtype: torch.dtype) -> None:
+    """Builds what ``maps_attention`` will launch for these sizes (at load, not in a step)."""
+
+
+def maps_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, maps, Dk, Dv, page_size, scale, window) -> None:
+    """Attention with ``maps`` maps a head (q [T, H, maps, Dk]; a cached key row holds a kv head's
+    maps side by side; one set of values a kv head), causal with an optional window; float32
+    results per map, [T, H, maps, Dv]."""
+    K.attention_kv_maps(ctx, q, k_cache, v_cache, out, table, H, Hkv, maps, Dk, Dv, page_size, scale, window)

@@ -1102,3 +1102,131 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
         shared.stride(0) if shared is not None else 0, out.data_ptr(), out.stride(0), T, top, n_out,
         _stream()), "moe_combine")
     return out
+
+
+def moe_route_scored(logits: torch.Tensor, groups: int, keep: int, top: int, route_scale: float,
+                     renormalize: bool, score_fn: str = "softmax", correction: Optional[torch.Tensor] = None,
+                     group_best: int = 1, norm_eps: float = 0.0):
+    """(ids int32 [T, top], weights float32 [T, top]) with every choice of the route kernel as an
+    argument: ``score_fn`` "softmax" or "sigmoid"; ``correction`` float32 [E], added to the scores
+    for the choice only; a group scores as the sum of its ``group_best`` largest choice scores;
+    ``norm_eps`` in the denominator of the renormalised weights."""
+    T, E = logits.shape
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=_F32, device=logits.device)
+    fn_code = {"softmax": 0, "sigmoid": 1}[score_fn]
+    L.check(L.core().slb_moe_route_scored(
+        logits.data_ptr(), logits.stride(0), T, E, groups, keep, top, float(route_scale),
+        1 if renormalize else 0, fn_code, _p(correction), int(group_best), float(norm_eps),
+        ids.data_ptr(), weights.data_ptr(), _stream()), "moe_route")
+    return ids, weights
+
+
+GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, activation: str = "silu") -> None:
+    """out[t, i] = act(gate_i) * up_i (layout as ``swiglu``); ``activation`` "silu" or "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))))."""
+    fn = getattr(L.core(), "slb_gated_act_" + _suffix(out.dtype))
+    L.check(fn(gate_up.data_ptr(), out.data_ptr(), out.shape[0], out.shape[1], gate_up.stride(0),
+               out.stride(0), int(block), GATED_ACTIVATIONS[activation], _stream()), "gated_act")
+
+
+# ------------------------------------------- several residual streams, embedding norm
+def hyper_max_streams() -> int:
+    return L.core().slb_hyper_max_streams()
+
+
+def embed_norm_streams(ids: torch.Tensor, table: torch.Tensor, weight: Optional[torch.Tensor], eps: float,
+                       out: torch.Tensor) -> None:
+    """out[t, s] = rmsnorm(table[ids[t]]) * weight for every stream s (weight None: the embedding
+    itself); out float32 [T, n, h] or [T, h]."""
+    n = out.shape[1] if out.dim() == 3 else 1
+    fn = getattr(L.core(), "slb_embed_norm_streams_" + _suffix(table.dtype))
+    L.check(fn(ids.data_ptr(), table.data_ptr(), _p(weight), float(eps), out.data_ptr(), ids.numel(), n,
+               table.shape[1], table.shape[0], _stream()), "embed_norm_streams")
+
+
+def hyper_mix_norm(streams: torch.Tensor, update: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+                   out_w: Optional[torch.Tensor], read_w: Optional[torch.Tensor],
+                   norm_w: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor],
+                   row_map: Optional[torch.Tensor] = None) -> None:
+    """``streams`` float32 [T, n, w]: with ``update`` [T, w], X_t <- sum_s mix[s, t] X_s + out_w[t] update
+    (in place; not written when ``row_map`` selects rows); then out[r] = rmsnorm(sum_s read_w[s] X_s)
+    * norm_w (``read_w`` None: the plain sum; ``norm_w`` None: no norm)."""
+    T, n, w = streams.shape
+    rows = T if row_map is None else row_map.numel()
+    dt = out.dtype if out is not None else update.dtype
+    fn = getattr(L.core(), "slb_hyper_mix_norm_" + _suffix(dt))
+    L.check(fn(streams.data_ptr(), _p(update), update.stride(0) if update is not None else 0, _p(mix),
+               _p(out_w), _p(read_w), _p(norm_w), float(eps), _p(out),
+               out.stride(0) if out is not None else 0, _p(row_map), rows, n, w, _stream()), "hyper_mix_norm")
+
+
+GATE_ACTIVATIONS = {None: 0, "sigmoid": 1, "silu": 2}
+
+
+def group_norm_gate(x: torch.Tensor, groups: int, size: int, out: torch.Tensor, *, eps: float,
+                    weight: Optional[torch.Tensor] = None, factor: float = 1.0,
+                    gate: Optional[torch.Tensor] = None, gate_activation: Optional[str] = None,
+                    maps: int = 1, lam: Optional[torch.Tensor] = None) -> None:
+    """out[t, g, :] = y / sqrt(mean(y^2) + eps) * weight * factor * act(gate) over ``groups`` groups of
+    ``size`` elements; y = x (float32 [T, groups * size]) or, with ``maps`` 2, x[t, g, 0] - lam *
+    x[t, g, 1] of x [T, groups, 2, size] (``lam`` a float32 scalar on the device)."""
+    fn = getattr(L.core(), "slb_group_norm_gate_" + _suffix(out.dtype))
+    L.check(fn(x.data_ptr(), x.stride(0), maps, _p(lam), _p(weight), float(eps), float(factor), _p(gate),
+               gate.stride(0) if gate is not None else 0, GATE_ACTIVATIONS[gate_activation if gate is not None else None],
+               out.data_ptr(), out.stride(0), x.shape[0], groups, size, _stream()), "group_norm_gate")
+
+
+# ----------------------------------------------- linear attention with a decay
+class _DecayAttnArgs(_ct.Structure):
+    _fields_ = [
+        ("proj", _ct.c_void_p), ("ld", _ct.c_int),
+        ("q_off", _ct.c_int), ("k_off", _ct.c_int), ("v_off", _ct.c_int),
+        ("H", _ct.c_int), ("D", _ct.c_int), ("Dv", _ct.c_int), ("act", _ct.c_int),
+        ("freq", _ct.c_void_p), ("rot_dims", _ct.c_int), ("k_scale", _ct.c_float),
+        ("decay", _ct.c_void_p),
+        ("positions", _ct.c_void_p), ("cu_q", _ct.c_void_p), ("state_slots", _ct.c_void_p),
+        ("state", _ct.c_void_p), ("num_slots", _ct.c_int),
+        ("out", _ct.c_void_p), ("ldo", _ct.c_int),
+    ]
+
+
+def decay_attention_max_dim() -> int:
+    return L.core().slb_decay_attention_max_dim()
+
+
+def decay_attention(proj: torch.Tensor, ctx, state: torch.Tensor, decay: torch.Tensor, out: torch.Tensor, *,
+                    q_off: int, k_off: int, v_off: int, num_heads: int, head_dim: int, value_dim: int,
+                    activation: Optional[str] = None, freq: Optional[torch.Tensor] = None, rot_dims: int = 0,
+                    key_scale: float = 1.0) -> None:
+    """o_t = S_t^T q_t with S_t = decay_h S_{t-1} + k_t v_t^T per head over the tokens of every request
+    of the step, in order; q, k, v are columns of ``proj`` [T, ...]; ``state`` float32
+    [slots, H, D, Dv] is read at ``ctx.state_slots`` and left advanced; ``out`` float32 [T, H * Dv]."""
+    a = _DecayAttnArgs()
+    a.proj, a.ld = proj.data_ptr(), proj.stride(0)
+    a.q_off, a.k_off, a.v_off = q_off, k_off, v_off
+    a.H, a.D, a.Dv = num_heads, head_dim, value_dim
+    a.act = {None: 0, "silu": 1}[activation]
+    a.freq, a.rot_dims, a.k_scale = _p(freq), rot_dims, float(key_scale)
+    a.decay = decay.data_ptr()
+    a.positions, a.cu_q, a.state_slots = ctx.positions.data_ptr(), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr()
+    a.state, a.num_slots = state.data_ptr(), state.shape[0]
+    a.out, a.ldo = out.data_ptr(), out.stride(0)
+    fn = getattr(L.core(), "slb_decay_attention_" + _suffix(proj.dtype))
+    L.check(fn(_ct.byref(a), ctx.num_seqs, _stream()), "decay_attention")
+
+
+def attention_kv_maps(ctx, q, k_cache, v_cache, out, block_table, num_heads: int, num_kv_heads: int,
+                      maps: int, k_dim: int, v_dim: int, page_size: int, scale: float, window: int = 0) -> None:
+    """The plain kernel with ``maps`` attention maps a head: q [T, H, maps, k_dim], cached key rows
+    [maps, k_dim] per kv head, one set of values per kv head; ``out`` float32 [T, H, maps, v_dim]."""
+    tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads, attention_kv_tile_rows())
+    fn = getattr(L.core(), "slb_attention_kv_maps_" + _suffix(q.dtype))
+    L.check(fn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), maps * k_dim, maps, v_cache.data_ptr(), v_dim,
+               out.data_ptr(), out.stride(0), block_table.data_ptr(), block_table.shape[1],
+               ctx.cu_q.data_ptr(), ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n,
+               num_heads, num_kv_heads, k_dim, v_dim, page_size, k_cache.shape[0], float(scale), int(window),
+               _stream()), "attention_kv_maps")

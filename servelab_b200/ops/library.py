@@ -75,6 +75,21 @@ _CORE_SIGNATURES = {
     "slb_gemm_simt_batched_bf16": [P, I, P, I, P, I, I, I, I, I, LL, LL, LL, P],
     "slb_moe_tile_rows": [],
     "slb_moe_route": [P, I, I, I, I, I, I, F, I, P, P, P],
+    "slb_moe_route_scored": [P, I, I, I, I, I, I, F, I, I, P, I, F, P, P, P],
+    "slb_gated_act_f32": [P, P, I, I, I, I, I, I, P],
+    "slb_gated_act_bf16": [P, P, I, I, I, I, I, I, P],
+    "slb_attention_kv_maps_f32": [P, I, P, I, I, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
+    "slb_attention_kv_maps_bf16": [P, I, P, I, I, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
+    "slb_hyper_max_streams": [],
+    "slb_embed_norm_streams_f32": [P, P, P, F, P, I, I, I, I, P],
+    "slb_embed_norm_streams_bf16": [P, P, P, F, P, I, I, I, I, P],
+    "slb_hyper_mix_norm_f32": [P, P, I, P, P, P, P, F, P, I, P, I, I, I, P],
+    "slb_hyper_mix_norm_bf16": [P, P, I, P, P, P, P, F, P, I, P, I, I, I, P],
+    "slb_group_norm_gate_f32": [P, I, I, P, P, F, F, P, I, I, P, I, I, I, I, P],
+    "slb_group_norm_gate_bf16": [P, I, I, P, P, F, F, P, I, I, P, I, I, I, I, P],
+    "slb_decay_attention_max_dim": [],
+    "slb_decay_attention_f32": [P, I, P],
+    "slb_decay_attention_bf16": [P, I, P],
     "slb_router_logits_f32": [P, I, P, I, P, I, I, I, I, P],
     "slb_router_logits_bf16": [P, I, P, I, P, I, I, I, I, P],
     "slb_moe_plan_ints": [I, I],

@@ -121,22 +121,26 @@ def qkv_projection(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Te
                      rotary_dim, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim)
 
 
-def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) for ``w_gate_up`` [2I, h]: gate rows then up rows
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int, activation: str = "silu") -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) (``activation`` "silu" or "gelu_tanh"; the product's own epilogue
+    knows SiLU only) for ``w_gate_up`` [2I, h]: gate rows then up rows
     (``block`` 0), or alternating in runs of ``block`` rows.  Decode steps in bfloat16
     apply the activation in the product's epilogue; everything else runs the product and
     then the activation kernel."""
     M = x.shape[0]
     inter = w_gate_up.shape[0] // 2
     xt = x.z if isinstance(x, K.ScaledRows) else x
-    if (fuse_swiglu and xt.dtype == torch.bfloat16 and block == K.SWIGLU_BLOCK
+    if (fuse_swiglu and activation == "silu" and xt.dtype == torch.bfloat16 and block == K.SWIGLU_BLOCK
             and K.tc_decode_splits(w_gate_up.shape[0], w_gate_up.shape[1],
                                    K.tc_token_groups(M, w_gate_up)) == 1
             and _tc_ok(xt, w_gate_up, M)):
         return K.gemm_tc_decode(x, w_gate_up, None, swiglu=True)
     gu = linear(x, w_gate_up)
     act = torch.empty((M, inter), dtype=x.dtype, device=x.device)
-    K.swiglu(gu, act, block)
+    if activation == "silu":
+        K.swiglu(gu, act, block)
+    else:
+        K.gated_act(K.plain_unless(None, gu), act, block, activation)
     return act
 
 

@@ -1,7 +1,8 @@
 """Parts that layers are put together from; importing registers the built-in kinds."""
 
-from . import (attention, block, conv_attention, feed_forward, latent_attention, norm,  # noqa: F401
-               normed_attention, position, routed_experts)                      # (registration)
+from . import (attention, block, conv_attention, decay_attention, differential_attention,  # noqa: F401
+               feed_forward, latent_attention, norm, normed_attention, position,
+               routed_experts)                                                  # (registration)
 from .base import (Block, BuildEnv, FeedForward, LayerCache, Mixer, Norm, Part,
                    PositionEncoding)
 from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, build_part, part_class,

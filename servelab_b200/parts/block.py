@@ -10,7 +10,8 @@ from __future__ import annotations
 
 from ..ops.kernels import plain_unless
 from .base import Block
-from .norm import PostNormed
+from ..weights.source import BIAS, MIXING, TensorDecl
+from .norm import HyperPending, PostNormed
 from .registry import FEED_FORWARDS, MIXERS, NORMS, build_part, part_class, register_block
 
 
@@ -169,6 +170,80 @@ class ResultNormBlock(Block):
         h = LayerNorm.close(ctx, resid, a, self.env.dtype)
         f = K_plain(self.feed_forward.forward(ctx, h))
         return resid, PostNormed(ctx, f, self.ff_post_norm)
+
+
+@register_block("hyper_connections")
+class HyperConnectionsBlock(Block):
+    """The residual is ``streams`` parallel copies X [T, n, w].  Sublayer f with norm N and the
+    learned vectors in, out [n] and matrix mix [n, n] (indexed [from, to]):
+
+        u = sum_s in[s] X_s;   y = f(N(u));   X_t <- sum_s mix[s, t] X_s + out[t] y   (all t at once)
+
+    A sublayer's y travels as a ``HyperPending`` value to the kernel that prepares the next
+    reader's input, which folds it in on the way.  ``feed_forward`` None: the layer ends after the
+    mixer."""
+    accepts_hyper_pending = True
+
+    @staticmethod
+    def _members(spec, prefix):
+        out = [(NORMS, spec.mixer_norm, f"{prefix}.{spec.mixer_norm_name}"),
+               (MIXERS, spec.mixer, f"{prefix}.{spec.mixer_name}")]
+        if spec.feed_forward is not None:
+            out += [(NORMS, spec.ff_norm, f"{prefix}.{spec.ff_norm_name}"),
+                    (FEED_FORWARDS, spec.feed_forward, f"{prefix}.{spec.feed_forward_name}")]
+        return tuple(out)
+
+    @staticmethod
+    def _hyper_names(spec, prefix):
+        names = [spec.mixer_hyper_name] + ([spec.ff_hyper_name] if spec.feed_forward is not None else [])
+        return [f"{prefix}.{n}" for n in names]
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        if spec.streams < 1:
+            raise ValueError("hyper_connections: at least one stream")
+        if spec.mixer_norm is None or (spec.feed_forward is not None and spec.ff_norm is None):
+            raise ValueError("hyper_connections: every sublayer needs a norm before it")
+        self._parts = [build_part(t, part, name, env) for t, part, name in self._members(spec, prefix)]
+        for norm in self._parts[0::2]:
+            if not hasattr(norm, "read_streams"):
+                raise ValueError(f"hyper_connections: the norm {norm.spec.kind!r} cannot read several streams")
+        self.mixer_norm, self.mixer = self._parts[:2]
+        self.ff_norm, self.feed_forward = self._parts[2:] if len(self._parts) > 2 else (None, None)
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in self._parts)
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        out = []
+        for table, part, name in cls._members(spec, prefix):
+            out += part_class(table, part).declare(part, name)
+        n = spec.streams
+        for h in cls._hyper_names(spec, prefix):
+            out += [TensorDecl(h + ".in", (n,), BIAS), TensorDecl(h + ".out", (n,), BIAS),
+                    TensorDecl(h + ".mix", (n, n), MIXING)]
+        return out
+
+    @classmethod
+    def cache_request(cls, spec):
+        return part_class(MIXERS, spec.mixer).cache_request(spec.mixer)
+
+    def load(self, store):
+        for p in self._parts:
+            p.load(store)
+        self.hyper = [(store.get(h + ".in"), store.get(h + ".mix").contiguous(), store.get(h + ".out"))
+                      for h in self._hyper_names(self.spec, self.prefix)]
+
+    def forward(self, ctx, streams, pending, cache, owns_cache):
+        if streams.dim() != 3 or streams.shape[1] != self.spec.streams:
+            raise ValueError("hyper_connections: the residual must be [tokens, streams, hidden]")
+        read, mix, out_w = self.hyper[0]
+        x = self.mixer_norm.read_streams(ctx, streams, pending, read)
+        pending = HyperPending(self.mixer.forward(ctx, x, cache, owns_cache), mix, out_w)
+        if self.feed_forward is None:
+            return streams, pending
+        read, mix, out_w = self.hyper[1]
+        x = self.ff_norm.read_streams(ctx, streams, pending, read)
+        return streams, HyperPending(self.feed_forward.forward(ctx, x), mix, out_w)
 
 
 def K_plain(value):

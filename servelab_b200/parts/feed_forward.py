@@ -23,8 +23,9 @@ class GatedMLP(FeedForward):
 
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
-        if spec.activation != "silu":
-            raise ValueError(f"gated_mlp: activation {spec.activation!r} has no kernel (silu only)")
+        if spec.activation not in K.GATED_ACTIVATIONS:
+            raise ValueError(f"gated_mlp: activation {spec.activation!r} has no kernel "
+                             f"({', '.join(K.GATED_ACTIVATIONS)})")
         if spec.bias:
             raise ValueError("gated_mlp: biases are not supported")
 
@@ -51,5 +52,5 @@ class GatedMLP(FeedForward):
         self.w_down = store.get(f"{self.prefix}.{self.spec.down_name}{sfx}")
 
     def forward(self, ctx, x):
-        act = gated_linear(x, self.w_gate_up, self.block)
+        act = gated_linear(x, self.w_gate_up, self.block, self.spec.activation)
         return linear(act, self.w_down, consumer="norm")

@@ -22,14 +22,30 @@ class RMSNorm(Norm):
     accepts_deferred_linear = True    # ... or a product not launched yet, which then runs with the
                                       # add and this norm in its epilogue; the result is ScaledRows
 
+    accepts_hyper_pending = True      # ... or the update of a residual kept as several streams
+
     @classmethod
     def declare(cls, spec, prefix):
-        return [TensorDecl(prefix + ".weight", (spec.dim,), NORM)]
+        return [TensorDecl(prefix + spec.weight_suffix, (spec.dim,), NORM)]
 
     def load(self, store):
-        self.weight = store.get(self.prefix + ".weight")
+        self.weight = store.get(self.prefix + self.spec.weight_suffix)
+
+    def read_streams(self, ctx, streams, pending, read_weights, out_rows=None):
+        """For a residual kept as streams [T, n, dim]: folds the pending update in (``HyperPending``
+        or None), then norms sum_s read_weights[s] x_s (None: the plain sum) -- one launch.  With
+        ``out_rows`` only those rows are produced and the streams are left as they are."""
+        rows = streams.shape[0] if out_rows is None else out_rows.numel()
+        out = torch.empty((rows, self.spec.dim), dtype=self.env.dtype, device=streams.device)
+        update = mix = out_w = None
+        if pending is not None:
+            update, mix, out_w = K.plain_unless(None, pending.value), pending.mix, pending.out_weights
+        K.hyper_mix_norm(streams, update, mix, out_w, read_weights, self.weight, self.spec.eps, out, out_rows)
+        return out
 
     def forward(self, ctx, resid, delta, out_rows=None):
+        if resid.dim() == 3:              # several streams: their sum is what a model's last norm reads
+            return self.read_streams(ctx, resid, delta, None, out_rows)
         if isinstance(delta, K.DeferredLinear):
             if out_rows is None and self.env.dtype == torch.bfloat16:
                 return K.gemm_tc_resid_norm(delta.x, delta.w, delta.bias, resid, self.weight,
@@ -39,6 +55,21 @@ class RMSNorm(Norm):
         out = torch.empty((rows, self.spec.dim), dtype=self.env.dtype, device=resid.device)
         K.add_rmsnorm(resid, delta, self.weight, self.spec.eps, out, out_rows)
         return out
+
+
+class HyperPending:
+    """A sublayer's result that has not been folded into a residual kept as several streams yet:
+    x_t <- sum_s mix[s, t] x_s + out_weights[t] value.  The kernel that prepares the next reader's
+    input does it on the way (``RMSNorm.read_streams``)."""
+
+    accept_flag = "accepts_hyper_pending"
+
+    def __init__(self, value, mix: torch.Tensor, out_weights: torch.Tensor):
+        self.value, self.mix, self.out_weights = value, mix, out_weights
+
+    def materialize(self):
+        raise TypeError("an update of several residual streams can only be handed to a part that folds "
+                        "it in (a norm with read_streams)")
 
 
 fuse_product_norms = True     # Dynamic Tanh: a deferred product runs with the norms in its epilogue

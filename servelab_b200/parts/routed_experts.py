@@ -28,6 +28,8 @@ class RoutedExperts(FeedForward):
             raise ValueError("routed_experts: experts must split into equal groups, 0 < keep <= groups")
         if not 0 < spec.top <= spec.num_experts // spec.num_groups * spec.keep_groups:
             raise ValueError("routed_experts: top experts must fit into the kept groups")
+        if spec.score_fn not in ("softmax", "sigmoid") or spec.group_best < 1:
+            raise ValueError("routed_experts: score_fn is 'softmax' or 'sigmoid'; group_best at least 1")
         self.shared = (build_part(FEED_FORWARDS, spec.shared, f"{prefix}.{spec.shared_name}", env)
                        if spec.shared is not None else None)
 
@@ -40,6 +42,8 @@ class RoutedExperts(FeedForward):
     def declare(cls, spec, prefix):
         h, i = spec.hidden_size, spec.expert_size
         out = [TensorDecl(f"{prefix}.{spec.router_name}{spec.weight_suffix}", (spec.num_experts, h), BIAS)]
+        if spec.correction_name:
+            out.append(TensorDecl(f"{prefix}.{spec.correction_name}", (spec.num_experts,), BIAS))
         for j in range(spec.num_experts):
             g, u, d = cls._expert(spec, prefix, j)
             out += [TensorDecl(g, (i, h), MATRIX), TensorDecl(u, (i, h), MATRIX), TensorDecl(d, (h, i), MATRIX)]
@@ -50,6 +54,7 @@ class RoutedExperts(FeedForward):
     def load(self, store):
         s = self.spec
         self.router = store.get(f"{self.prefix}.{s.router_name}{s.weight_suffix}")      # float32
+        self.correction = store.get(f"{self.prefix}.{s.correction_name}") if s.correction_name else None
         names = [self._expert(s, self.prefix, j) for j in range(s.num_experts)]
         # [E, 2 I, h]: an expert's gate rows, then its up rows; [E, h, I]
         self.w_gate_up = torch.stack([torch.cat([store.get(g), store.get(u)]) for g, u, _ in names]).contiguous()
@@ -61,6 +66,11 @@ class RoutedExperts(FeedForward):
         s = self.spec
         x = K.plain_unless(None, x)
         logits = K.router_logits(x, self.router)
-        ids, weights = K.moe_route(logits, s.num_groups, s.keep_groups, s.top, s.route_scale, s.renormalize)
+        if s.score_fn == "softmax" and self.correction is None and s.group_best == 1 and s.norm_eps == 0.0:
+            ids, weights = K.moe_route(logits, s.num_groups, s.keep_groups, s.top, s.route_scale, s.renormalize)
+        else:
+            ids, weights = K.moe_route_scored(logits, s.num_groups, s.keep_groups, s.top, s.route_scale,
+                                              s.renormalize, s.score_fn, self.correction, s.group_best,
+                                              s.norm_eps)
         shared = K.plain_unless(None, self.shared.forward(ctx, x)) if self.shared is not None else None
         return K.moe_experts(x, ids, weights, self.w_gate_up, self.w_down, shared)
