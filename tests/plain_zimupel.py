@@ -252,3 +252,13 @@ def load_folder(folder: str):
     with open(f"{folder}/config.json") as f:
         cfg = json.load(f)
     return cfg, read_safetensors(f"{folder}/model.safetensors")
+
+
+def greedy(cfg: dict, W: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    """``n_new`` tokens by arg-max, the whole sequence recomputed for every token."""
+    ids, out = list(prompt), []
+    for _ in range(n_new):
+        t = int(forward(cfg, W, ids)[-1].argmax())
+        out.append(t)
+        ids.append(t)
+    return out
