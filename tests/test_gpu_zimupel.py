@@ -1,0 +1,578 @@
+"""Zimupel on the GPU against the plain implementation (``plain_zimupel``): every new kernel
+alone, then whole models replayed whole, token by token, in portions down to two tokens and in
+mixed batches with pages and slots used again, in float32 and bfloat16, and greedy generation
+through the engine."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_zimupel as plain
+import zimupel_cases as C
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+F64 = torch.float64
+
+
+def _ctx(entries, groups=1):
+    from servelab_b200.engine.batch import StepContext
+    return StepContext.pack(entries, groups, DEV)
+
+
+def _entry(tokens, start, table=(), slot=0):
+    from servelab_b200.engine.batch import BatchEntry
+    return BatchEntry(tokens=[0] * tokens, start=start, want=(), block_tables=[list(table)], state_slot=slot)
+
+
+# ------------------------------------------------- embedding norm and streams
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n, h", [(1, 50), (3, 48), (4, 1030)])
+def test_embedding_norm_and_copies(dtype, n, h):
+    from servelab_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(h)
+    table = torch.randn(37, h, generator=g).to(dtype)
+    w = torch.randn(h, generator=g)
+    ids = torch.tensor([5, 0, 36, 5, 17], dtype=torch.int32)
+    out = torch.empty(5, n, h, dtype=torch.float32, device=DEV)
+    K.embed_norm_streams(ids.to(DEV), table.to(DEV), w.to(DEV), 1e-5, out)
+    want = plain.rms_norm(table.double()[ids.long()], w.double(), 1e-5)
+    for s in range(n):
+        assert (out[:, s].cpu().double() - want).abs().max() < 1e-5
+    K.embed_norm_streams(ids.to(DEV), table.to(DEV), None, 0.0, out)       # no norm: the rows themselves
+    assert torch.equal(out[:, n - 1].cpu(), table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n, w", [(1, 50), (2, 48), (3, 256), (8, 77), (4, 5000)])
+def test_streams_fold_read_and_norm(dtype, n, w):
+    """X_t <- sum_s M[s, t] X_s + b_t y; u = sum_s a_s X_s; out = rmsnorm(u) * weight -- against the
+    plain expressions, with a mixing matrix that is far from symmetric (so [from, to] shows)."""
+    from servelab_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(n * 1000 + w)
+    T = 6
+    X = torch.randn(T, n, w, generator=g) * 2
+    y = torch.randn(T, w, generator=g).to(dtype)
+    M = torch.randn(n, n, generator=g)
+    b, a, nw = torch.randn(n, generator=g), torch.randn(n, generator=g), torch.randn(w, generator=g)
+    Xn = torch.einsum("sr,tsw->trw", M.double(), X.double()) + b.double()[None, :, None] * y.double()[:, None, :]
+    u = torch.einsum("s,tsw->tw", a.double(), Xn)
+    want = plain.rms_norm(u, nw.double(), 1e-5)
+    tol = 2e-5 if dtype == torch.float32 else 4e-2
+    x = X.to(DEV)
+    out = torch.empty(T, w, dtype=dtype, device=DEV)
+    K.hyper_mix_norm(x, y.to(DEV), M.to(DEV), b.to(DEV), a.to(DEV), nw.to(DEV), 1e-5, out)
+    assert (x.cpu().double() - Xn).abs().max() < 2e-5 * max(1.0, float(Xn.abs().max()))
+    assert (out.cpu().double() - want).abs().max() < tol * max(1.0, float(want.abs().max()))
+    # selected rows, the plain sum of the streams (a model's last norm): the streams stay as they are
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    x2 = X.to(DEV)
+    out2 = torch.empty(2, w, dtype=dtype, device=DEV)
+    K.hyper_mix_norm(x2, y.to(DEV), M.to(DEV), b.to(DEV), None, nw.to(DEV), 1e-5, out2, rows)
+    want2 = plain.rms_norm(Xn.sum(1), nw.double(), 1e-5)[[4, 1]]
+    assert torch.equal(x2.cpu(), X)
+    assert (out2.cpu().double() - want2).abs().max() < tol * max(1.0, float(want2.abs().max()))
+    # nothing pending: a read and a norm
+    out3 = torch.empty(T, w, dtype=dtype, device=DEV)
+    K.hyper_mix_norm(x2, None, None, None, a.to(DEV), nw.to(DEV), 1e-5, out3)
+    want3 = plain.rms_norm(torch.einsum("s,tsw->tw", a.double(), X.double()), nw.double(), 1e-5)
+    assert (out3.cpu().double() - want3).abs().max() < tol * max(1.0, float(want3.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_over_heads_or_the_row_with_a_gate(dtype):
+    from servelab_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(3)
+    T, Hh, Dv = 7, 3, 40
+    x = torch.randn(T, Hh * Dv, generator=g) * torch.tensor([0.01, 1.0, 100.0]).repeat_interleave(Dv)
+    gate = torch.randn(T, Hh * Dv + 8, generator=g).to(dtype)
+    w = torch.randn(Hh * Dv, generator=g)
+    gd = gate.double()[:, 3:3 + Hh * Dv]
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    out = torch.empty(T, Hh * Dv, dtype=dtype, device=DEV)
+    # per head, no weight, SiLU gate: heads of very different size come out alike
+    K.group_norm_gate(x.to(DEV), Hh, Dv, out, eps=1e-6, gate=gate.to(DEV)[:, 3:3 + Hh * Dv], gate_activation="silu")
+    want = plain.rms_norm(x.double().view(T, Hh, Dv), None, 1e-6).reshape(T, -1) * plain.silu(gd)
+    assert (out.cpu().double() - want).abs().max() < tol * max(1.0, float(want.abs().max()))
+    # the whole row with a weight, sigmoid gate
+    K.group_norm_gate(x.to(DEV), 1, Hh * Dv, out, eps=1e-6, weight=w.to(DEV), gate=gate.to(DEV)[:, 3:3 + Hh * Dv],
+                      gate_activation="sigmoid")
+    want = plain.rms_norm(x.double(), w.double(), 1e-6) * torch.sigmoid(gd)
+    assert (out.cpu().double() - want).abs().max() < tol * max(1.0, float(want.abs().max()))
+    # two maps side by side: a_1 - lambda a_2, normed per head, times a factor, no gate
+    maps = torch.randn(T, Hh, 2, Dv, generator=g)
+    lam = torch.tensor([0.7])
+    K.group_norm_gate(maps.view(T, -1).to(DEV), Hh, Dv, out, eps=1e-5, factor=0.4, maps=2, lam=lam.to(DEV))
+    want = plain.rms_norm(maps.double()[:, :, 0] - 0.7 * maps.double()[:, :, 1], None, 1e-5).reshape(T, -1) * 0.4
+    assert (out.cpu().double() - want).abs().max() < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gelu_gated_activation(dtype):
+    from servelab_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(4)
+    for inter, block in ((40, 0), (22, 0), (128, 64), (7, 0)):
+        gu = (torch.randn(5, 2 * inter, generator=g) * 2).to(dtype)
+        out = torch.empty(5, inter, dtype=dtype, device=DEV)
+        K.gated_act(gu.to(DEV), out, block, "gelu_tanh")
+        d = gu.double()
+        if block:
+            d = d.view(5, inter // block, 2, block)
+            gate, up = d[:, :, 0].reshape(5, inter), d[:, :, 1].reshape(5, inter)
+        else:
+            gate, up = d[:, :inter], d[:, inter:]
+        want = plain.gelu_tanh(gate) * up
+        assert (out.cpu().double() - want).abs().max() < (1e-5 if dtype == torch.float32 else 5e-2)
+        K.gated_act(gu.to(DEV), out, block, "silu")
+        assert (out.cpu().double() - plain.silu(gate) * up).abs().max() < (1e-5 if dtype == torch.float32 else 5e-2)
+
+
+# ------------------------------------------------------------------ the router
+@pytest.mark.parametrize("E, groups, keep, top", [(8, 2, 1, 2), (6, 3, 2, 2), (12, 4, 3, 5), (5, 1, 1, 5),
+                                                  (4, 4, 2, 2), (9, 3, 1, 1), (64, 8, 4, 8)])
+def test_route_kernel_against_the_plain_router(E, groups, keep, top):
+    """Sigmoid scores, offsets in the choice only, groups by the sum of their two best (a group of
+    one expert: that one), weights renormalised; offsets so negative that every choice score is
+    below zero, where an expert shut out as 0 instead of minus infinity would win."""
+    from servelab_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(E * 100 + top)
+    T = 300
+    z = torch.randn(T, E, generator=g) * 2
+    for shift in (0.0, -3.0):
+        corr = torch.randn(E, generator=g) * 0.5 + shift
+        r = {"experts": E, "top": top}
+        if groups > 1:
+            r["groups"] = {"count": groups, "keep": keep}
+        want_ids, want_w = plain.route(z.double(), corr.double(), r)
+        ids, w = K.moe_route_scored(z.to(DEV), groups, keep, top, 1.0, True, "sigmoid", corr.to(DEV), 2, 1e-20)
+        # rows where float32 and float64 may order two nearly equal scores differently are left out
+        c = torch.sigmoid(z.double()) + corr.double()
+        gaps = (c[:, :, None] - c[:, None, :]).abs() + torch.eye(E, dtype=F64) * 9
+        clear = gaps.flatten(1).min(1).values > 1e-5
+        assert int(clear.sum()) > 0.9 * T
+        got_sorted, order = ids.cpu().long().sort(1)
+        want_sorted, worder = want_ids.sort(1)
+        assert torch.equal(got_sorted[clear], want_sorted[clear])
+        assert (w.cpu().double().gather(1, order) - want_w.gather(1, worder))[clear].abs().max() < 1e-6
+        assert (w.sum(1).cpu() - 1).abs().max() < 1e-5
+
+
+def test_softmax_route_is_still_the_old_one():
+    """The softmax router whose groups score as their best expert through both entry points."""
+    from servelab_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(8)
+    z = torch.randn(100, 12, generator=g) * 2
+    a = K.moe_route(z.to(DEV), 4, 2, 3, 1.7, False)
+    b = K.moe_route_scored(z.to(DEV), 4, 2, 3, 1.7, False, "softmax", None, 1, 0.0)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    s = torch.softmax(z.double(), -1)
+    gbest = s.view(100, 4, 3).max(-1).values.topk(2, -1).indices
+    allowed = torch.zeros(100, 4, dtype=torch.bool).scatter_(1, gbest, True).repeat_interleave(3, 1)
+    want = torch.where(allowed, s, torch.full_like(s, -1.0)).topk(3, -1)
+    assert torch.equal(a[0].cpu().long(), want.indices)
+    assert (a[1].cpu().double() - want.values * 1.7).abs().max() < 1e-6
+
+
+# ------------------------------------------------- the recurrence with a decay
+def _decay_case(seed, Hh, D, Dv, lens, dtype, act=None, rot=None, starts=None):
+    g = torch.Generator().manual_seed(seed)
+    T = sum(lens)
+    width = 2 * Hh * D + Hh * Dv + 3
+    proj = (torch.randn(T, width, generator=g) * 0.7).to(dtype)
+    decay = torch.rand(Hh, generator=g) * 0.2 + 0.8
+    decay[0] = 1.0
+    return proj, decay
+
+
+def _decay_want(proj, decay, Hh, D, Dv, lens, act, rot, key_scale):
+    """Every request from position 0, the oracle's closed form."""
+    out, t0 = [], 0
+    for n in lens:
+        p = proj[t0:t0 + n].double()
+        q, k = p[:, :Hh * D].view(n, Hh, D), p[:, Hh * D:2 * Hh * D].view(n, Hh, D)
+        v = p[:, 2 * Hh * D:2 * Hh * D + Hh * Dv].view(n, Hh, Dv)
+        if act:
+            q, k, v = plain.silu(q), plain.silu(k), plain.silu(v)
+        if rot:
+            q = plain.rotate_halves(q, torch.arange(n), rot[1], rot[0])
+            k = plain.rotate_halves(k, torch.arange(n), rot[1], rot[0])
+        out.append(plain.decayed_sum(q, k * key_scale, v, decay.double().tolist()).reshape(n, Hh * Dv))
+        t0 += n
+    return torch.cat(out)
+
+
+def _run_decay(proj, decay, state, Hh, D, Dv, pieces, act, rot, key_scale):
+    """``pieces``: per step a list of (request, tokens); requests are laid out one after the other in
+    ``proj`` and own the state slot of their number.  Returns the outputs in ``proj``'s order."""
+    from servelab_b200.ops import kernels as K
+    lens = {}
+    for step in pieces:
+        for r, n in step:
+            lens[r] = lens.get(r, 0) + n
+    base, acc = {}, 0
+    for r in sorted(lens):
+        base[r] = acc
+        acc += lens[r]
+    done = {r: 0 for r in lens}
+    out_all = torch.zeros(acc, Hh * Dv, dtype=torch.float32, device=DEV)
+    freq = None
+    if rot:
+        freq = (rot[0] ** (-2.0 * torch.arange(rot[1] // 2, dtype=F64) / rot[1])).float().to(DEV)
+    for step in pieces:
+        rows = torch.cat([torch.arange(base[r] + done[r], base[r] + done[r] + n) for r, n in step])
+        ctx = _ctx([_entry(n, done[r], slot=r) for r, n in step])
+        out = torch.empty(len(rows), Hh * Dv, dtype=torch.float32, device=DEV)
+        K.decay_attention(proj[rows].contiguous().to(DEV), ctx, state, decay.to(DEV), out, q_off=0, k_off=Hh * D,
+                          v_off=2 * Hh * D, num_heads=Hh, head_dim=D, value_dim=Dv, activation=act, freq=freq,
+                          rot_dims=rot[1] if rot else 0, key_scale=key_scale)
+        out_all[rows.to(DEV)] = out
+        for r, n in step:
+            done[r] += n
+    return out_all.cpu().double()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(3, 8, 12, None, None), (2, 16, 8, None, (500.0, 8)), (1, 24, 40, "silu", None),
+                                   (2, 64, 64, None, (10000.0, 64)), (3, 10, 6, "silu", (900.0, 4)),
+                                   (2, 128, 96, "silu", None), (1, 256, 33, None, (1e6, 128))])
+def test_decay_attention_whole_in_portions_and_token_by_token(dtype, shape):
+    """Three requests of unequal length in one batch, against the closed form; then the same cut
+    into portions (down to two tokens and one) with the state carried in slots, which must give
+    the same bits; slots are not cleared by the kernel, so a used slot is zeroed by the test as
+    the cache does."""
+    Hh, D, Dv, act, rot = shape
+    lens = [37, 5, 70]
+    proj, decay = _decay_case(D + Dv, Hh, D, Dv, lens, dtype)
+    ks = D ** -0.5
+    want = _decay_want(proj, decay, Hh, D, Dv, lens, act, rot, ks)
+    state = torch.full((5, Hh, D, Dv), 7.0, dtype=torch.float32, device=DEV)
+    state[:3] = 0
+    whole = _run_decay(proj, decay, state, Hh, D, Dv, [[(0, 37), (1, 5), (2, 70)]], act, rot, ks)
+    tol = 2e-5 if dtype == torch.float32 else 2e-5      # (the inputs are rounded, the arithmetic is float32)
+    assert (whole - want).abs().max() < tol * max(1.0, float(want.abs().max()))
+    assert torch.all(state[3:] == 7.0)                   # other slots untouched
+    final = state[:3].clone()
+    state[:3] = 0
+    pieces = [[(0, 7), (2, 2)], [(2, 33), (0, 1)], [(0, 2), (1, 5), (2, 1)], [(0, 27), (2, 34)]]
+    cut = _run_decay(proj, decay, state, Hh, D, Dv, pieces, act, rot, ks)
+    assert torch.equal(cut, whole) and torch.equal(state[:3], final)
+    state[:3] = 0
+    single = _run_decay(proj, decay, state, Hh, D, Dv,
+                        [[(0, 30), (1, 4), (2, 60)]] + [[(0, 1), (2, 1)]] * 7 + [[(1, 1), (2, 1)]] + [[(2, 1)]] * 2,
+                        act, rot, ks)
+    assert torch.equal(single, whole)
+
+
+def test_decay_attention_keeps_a_key_from_far_back():
+    """A head without decay must still answer to a key 1,500 tokens back whose value stands out; a
+    head with a fast decay must have forgotten it."""
+    Hh, D, Dv, n = 2, 16, 8, 1600
+    proj = torch.zeros(n, 2 * Hh * D + Hh * Dv)
+    g = torch.Generator().manual_seed(2)
+    proj[:, :] = torch.randn(n, proj.shape[1], generator=g) * 0.01
+    for h in range(Hh):
+        proj[100, Hh * D + h * D] = 5.0                  # the key at position 100: one large element
+        proj[100, 2 * Hh * D + h * Dv:2 * Hh * D + (h + 1) * Dv] = 3.0
+        proj[n - 1, h * D] = 5.0                         # the last query asks for it
+    decay = torch.tensor([1.0, 0.9])
+    state = torch.zeros(1, Hh, D, Dv, dtype=torch.float32, device=DEV)
+    out = _run_decay(proj, decay, state, Hh, D, Dv, [[(0, 1000)], [(0, 599)], [(0, 1)]], None, None, 1.0)
+    want = _decay_want(proj, decay, Hh, D, Dv, [n], None, None, 1.0)
+    assert (out - want).abs().max() < 5e-6 * float(want.abs().max())       # (float32 sums of 1,600 terms)
+    assert out[n - 1, :Dv].min() > 70 and out[n - 1, Dv:].abs().max() < 1.0
+
+
+# ---------------------------------------------- attention with two maps a head
+def _maps_case(seed, Hq, G, D, Dv, ctxs, qlens, ps, dtype, spike=None):
+    """Requests with contexts ``ctxs`` whose last ``qlens`` tokens are this step's queries; keys
+    [G, 2, D] and values [G, Dv] in pages in a shuffled order, unwritten slots hold 1e30.  ``spike``
+    = distance: in map 2 the key at that distance from every query gets a score far above the
+    others and a value of its own."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum(-(-c // ps) for c in ctxs) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    kc = torch.full((n_pages, G, ps, 2 * D), 1e30, dtype=dtype)
+    vc = torch.full((n_pages, G, ps, Dv), 1e30, dtype=dtype)
+    qs, wants, entries = [], [], []
+    rep = Hq // G
+    for c, n in zip(ctxs, qlens):
+        k = (torch.randn(c, G, 2, D, generator=g) * 0.5).to(dtype)
+        v = torch.randn(c, G, Dv, generator=g).to(dtype)
+        q = (torch.randn(n, Hq, 2, D, generator=g) * 0.5).to(dtype)
+        if spike is not None:
+            for i in range(n):
+                j = c - n + i - spike
+                if j >= 0:
+                    k[j, :, 1] = 3.0
+                    v[j] = 10.0 + i
+            q[:, :, 1] = 3.0 / D * 8
+        table, order = order[:-(-c // ps)], order[-(-c // ps):]
+        for p in range(c):
+            kc[table[p // ps], :, p % ps] = k[p].reshape(G, 2 * D)
+            vc[table[p // ps], :, p % ps] = v[p]
+        kk = k.double().repeat_interleave(rep, dim=1)
+        vv = v.double().repeat_interleave(rep, dim=1)
+        full_q = torch.zeros(c, Hq, 2, D, dtype=F64)
+        full_q[c - n:] = q.double()
+        a = torch.stack([plain.causal_softmax(full_q[:, :, m], kk[:, :, m], vv, 0.3)[c - n:] for m in (0, 1)], dim=2)
+        qs.append(q.reshape(n, -1))
+        wants.append(a.reshape(n, -1))                       # [n, Hq, 2, Dv]
+        entries.append(_entry(n, c - n, table))
+    return torch.cat(qs), kc, vc, torch.cat(wants), entries
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(4, 2, 16, 8, 8), (3, 3, 10, 6, 4), (4, 1, 64, 128, 16), (2, 1, 48, 96, 16)])
+@pytest.mark.parametrize("spike", [None, 0, 1, 33, 290])
+def test_attention_with_two_maps(dtype, shape, spike):
+    """Portions of unequal requests and single tokens in one batch; a key made dominant in the second
+    map only at the query itself, one back, across page and tile borders and 290 tokens back."""
+    from servelab_b200.ops import attention as A
+    Hq, G, D, Dv, ps = shape
+    ctxs, qlens = [300, 41, 1, 333, 64], [9, 41, 1, 1, 33]
+    q, kc, vc, want, entries = _maps_case(17 + D, Hq, G, D, Dv, ctxs, qlens, ps, dtype, spike)
+    ctx = _ctx(entries)
+    out = torch.empty(q.shape[0], Hq * 2 * Dv, dtype=torch.float32, device=DEV)
+    A.maps_attention(ctx, q.to(DEV), kc.to(DEV), vc.to(DEV), out, ctx.block_tables[0], Hq, G, 2, D, Dv, ps, 0.3, 0)
+    tol = 3e-5 if dtype == torch.float32 else 3e-2
+    assert (out.cpu().double() - want).abs().max() < tol * max(1.0, float(want.abs().max()))
+    if spike is not None:                # the second map of the single token after 332 others found its key
+        row = sum(qlens[:3])
+        assert out.view(-1, Hq, 2, Dv)[row, 0, 1].min() > 9.9 and out.view(-1, Hq, 2, Dv)[row, 0, 0].max() < 9
+
+
+# ------------------------------------------------------------ whole models
+LENGTHS = [70, 45, 190, 33, 2, 1, 58]
+TOL = {"float32": 5e-5, "bfloat16": 3e-2}       # of the largest logit
+
+
+@pytest.fixture(scope="module", params=["P", "Q", "R", "S"])
+def model(request, tmp_path_factory):
+    cfg, seed, page = C.CASES[request.param]
+    folder = C.make_model(str(tmp_path_factory.mktemp(f"zim_{request.param}")), cfg, seed)
+    reqs = {f"r{i}": H.random_ids(n, cfg["vocab"], 100 * seed + i) for i, n in enumerate(LENGTHS)}
+    pc, pw = plain.load_folder(folder)
+    ref = {rid: plain.forward(pc, pw, ids).float().numpy() for rid, ids in reqs.items()}
+    return {"name": request.param, "cfg": cfg, "folder": folder, "page": page, "requests": reqs,
+            "ref": ref, "plain": (pc, pw)}
+
+
+def _bulk_tail(requests, tail):
+    steps = H.trace_bulk_tail(requests, tail=tail)
+    last = {}
+    for st in steps:
+        for e in st["entries"]:
+            last[e["id"]] = st
+    for rid, st in last.items():
+        if rid not in st["end"]:
+            st["end"].append(rid)
+    return steps
+
+
+def _replay(model, dtype, steps, max_tokens=None, **kw):
+    from servelab_b200.replay import TraceSession
+    sess = TraceSession(model["folder"], dtype, max_tokens or H.peak_tokens(steps), page_size=model["page"],
+                        max_live=4, poison_cache=True, **kw)
+    got = H.collect(steps, H.run_session(sess, steps), model["cfg"]["vocab"])
+    sess.cache.check_invariants()
+    assert not sess.held and all(p.num_free() == p.num_pages for p in sess.cache.pools)
+    assert sess.cache.slots.num_free() == 4
+    return got, sess
+
+
+_WHOLE_BF16 = {}
+
+
+def _compare(model, dtype, got):
+    """float32: every position within the bound of the oracle.  bfloat16 in a model this small is
+    noisy, and a router's choice between two experts of nearly equal score may fall the other way
+    under rounding, which moves a position's logits far more than rounding does.  So bfloat16 is
+    held to the oracle loosely (median and upper quartile of the error), and tightly to the
+    bfloat16 logits of the same requests run WHOLE, which any schedule must reproduce up to the
+    order of its sums: a fault of the cache, the state, the pages or the batch shows there."""
+    scale = max(float(np.abs(r).max()) for r in model["ref"].values())
+    bound = TOL[dtype] * max(1.0, scale)
+    errs, first = [], None
+    for rid, ids in model["requests"].items():
+        assert sorted(got[rid]) == list(range(len(ids))), f"{rid}: positions missing"
+        for pos in range(len(ids)):
+            err = float(np.abs(got[rid][pos] - model["ref"][rid][pos]).max())
+            if err > bound and first is None:
+                first = (rid, pos, err)
+            errs.append(err)
+    errs = np.asarray(errs)
+    over = int((errs > bound).sum())
+    print(f"config {model['name']} {dtype}: worst abs logit error {errs.max():.3e}, median {np.median(errs):.3e}, "
+          f"{over} of {len(errs)} beyond {bound:.3e} (logits up to {scale:.2f})")
+    if dtype == "float32":
+        assert over == 0, (f"config {model['name']}: {over} positions beyond the bound; first: request "
+                           f"{first[0]} position {first[1]} (err {first[2]:.3e})")
+        return
+    assert np.median(errs) <= bound and np.percentile(errs, 75) <= 2.5 * bound
+    whole = _WHOLE_BF16.get(model["name"])
+    if whole is None:
+        whole = _WHOLE_BF16[model["name"]] = _replay(model, "bfloat16", H.trace_whole(model["requests"]))[0]
+    diffs = np.asarray([float(np.abs(got[rid][pos] - whole[rid][pos]).max())
+                        for rid, ids in model["requests"].items() for pos in range(len(ids))])
+    far = int((diffs > 0.5 * bound).sum())
+    print(f"   against the whole prompts in bfloat16: worst {diffs.max():.3e}, {far} beyond {0.5 * bound:.3e}")
+    assert far <= 0.03 * len(diffs), f"{far} positions differ from the whole-prompt run"
+
+
+def test_the_residual_after_every_layer(model):
+    """The sum of the streams (the one residual of a model without them) once a layer's last
+    update is folded in, against the oracle's."""
+    from servelab_b200.ops import kernels as K
+    from servelab_b200.replay import TraceSession
+    pc, pw = model["plain"]
+    ids = model["requests"]["r1"]
+    _, want = plain.forward(pc, pw, ids, True)
+    sess = TraceSession(model["folder"], "float32", 64, page_size=model["page"])
+    seen = []
+    for block in sess.runner.model.blocks:
+        def fwd(ctx, resid, delta, cache, owns, _f=block.forward):
+            resid, delta = _f(ctx, resid, delta, cache, owns)
+            if resid.dim() == 3:
+                closed = resid.clone()
+                total = torch.empty(resid.shape[0], resid.shape[2], dtype=torch.float32, device=resid.device)
+                K.hyper_mix_norm(closed, K.plain_unless(None, delta.value), delta.mix, delta.out_weights, None,
+                                 None, 0.0, total)
+                seen.append(total.double().cpu())
+            else:
+                seen.append((resid + K.plain_unless(None, delta)).double().cpu())
+            return resid, delta
+        block.forward = fwd
+    sess.run_step({"step": 0, "entries": [{"id": "x", "tokens": ids, "want": []}], "end": ["x"]})
+    assert len(seen) == len(want)
+    for i, (got, ref) in enumerate(zip(seen, want)):
+        assert (got - ref).abs().max() < 1e-4 * max(1.0, float(ref.abs().max())), f"layer {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole(model, dtype):
+    got, _ = _replay(model, dtype, H.trace_whole(model["requests"]))
+    _compare(model, dtype, got)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_then_token_by_token(model, dtype):
+    """The last 120 tokens one by one: long decoding through the state slots and the pages."""
+    got, _ = _replay(model, dtype, _bulk_tail(model["requests"], 120))
+    _compare(model, dtype, got)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions_down_to_two_tokens(model, dtype):
+    got, _ = _replay(model, dtype, H.trace_portions(model["requests"]))
+    _compare(model, dtype, got)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_with_pages_and_slots_used_again(model, dtype):
+    steps = H.trace_mixed(model["requests"], seed=4)
+    need = H.peak_tokens(steps)
+    assert need < sum(-(-len(v) // 64) * 64 for v in model["requests"].values())
+    assert len(model["requests"]) > 4                       # more requests than slots
+    got, _ = _replay(model, dtype, steps, need)
+    _compare(model, dtype, got)
+
+
+def test_float32_logits_do_not_depend_on_the_cut(model):
+    whole, _ = _replay(model, "float32", H.trace_whole(model["requests"]))
+    for steps in (H.trace_portions(model["requests"]), H.trace_mixed(model["requests"], seed=9),
+                  _bulk_tail(model["requests"], 40)):
+        got, _ = _replay(model, "float32", steps)
+        for rid in whole:
+            for pos in whole[rid]:
+                assert np.abs(got[rid][pos] - whole[rid][pos]).max() <= 2e-6, (rid, pos)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_single_token_steps_through_replayed_graphs(model, dtype):
+    steps = _bulk_tail(model["requests"], 40)
+    eager, _ = _replay(model, dtype, steps)
+    graphs, sess = _replay(model, dtype, steps, cuda_graphs=True)
+    assert sess.runner.graph_replays > 0
+    for rid in eager:
+        for pos in eager[rid]:
+            assert np.abs(graphs[rid][pos] - eager[rid][pos]).max() <= (2e-6 if dtype == "float32" else 2e-1)
+    _compare(model, dtype, graphs)
+
+
+def test_the_trace_runner_as_a_program(model, tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    steps = H.trace_mixed(model["requests"], seed=21)
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model["folder"], "--dtype", "bfloat16",
+         "--out", str(out), "--max-tokens", str(H.peak_tokens(steps)), "--page-size", str(model["page"])],
+        input="".join(json.dumps(st) + "\n" for st in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [ln for ln in proc.stdout.splitlines() if ln.startswith("done ")] == [f"done {st['step']}" for st in steps]
+    V = model["cfg"]["vocab"]
+    outputs = {st["step"]: np.fromfile(out / f"{st['step']}.f32", dtype="<f4").reshape(-1, V)
+               for st in steps if any(e["want"] for e in st["entries"])}
+    _compare(model, "bfloat16", H.collect(steps, outputs, V))
+
+
+# --------------------------------------------------------------- generation
+def _engine(model, dtype="float32", num_blocks=256, budget=2048, **kw):
+    from servelab_b200.config import CacheConfig, SchedulerConfig
+    from servelab_b200.engine.llm_engine import LLMEngine
+    return LLMEngine(model["folder"], CacheConfig(block_size=model["page"], num_blocks=num_blocks),
+                     SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=budget), dtype=dtype, **kw)
+
+
+def test_greedy_generation_through_the_engine(model):
+    """The entry point and its scheduler (continuous batching, portions under a token budget,
+    graphs, look-ahead) generate what the oracle generates, also with so few pages that requests
+    are preempted and recomputed (their state slots start from zero again)."""
+    from servelab_b200.sampling import SamplingParams
+    pc, pw = model["plain"]
+    prompts = [model["requests"][r][:n] for r, n in (("r0", 41), ("r1", 3), ("r2", 77), ("r5", 1), ("r3", 20))]
+    n_new = 14
+    want = [plain.greedy(pc, pw, p, n_new) for p in prompts]
+    sp = SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True)
+    outs = _engine(model).generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in outs] == want
+    outs = _engine(model, budget=16, cuda_graphs=False).generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in outs] == want
+    few = -(-(77 + n_new) // model["page"]) + 2
+    eng = _engine(model, num_blocks=few, budget=24)
+    outs = eng.generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in outs] == want
+    eng.runner.cache.check_invariants()
+    st = eng.stats()
+    assert st["running"] == 0 and st["pages_used"] == [0] * len(st["pages_used"])
+
+
+def test_command_line(model, tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    if model["name"] != "P":
+        pytest.skip("one configuration is enough for the command line")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pc, pw = model["plain"]
+    want = plain.greedy(pc, pw, [3, 1, 4, 1, 5], 6)
+    r = subprocess.run([sys.executable, "-m", "servelab_b200", "--model", model["folder"],
+                        "--prompt-ids", "3,1,4,1,5", "--max-tokens", "6", "--temperature", "0",
+                        "--dtype", "float32", "--ignore-eos", "--block-size", "8", "--num-blocks", "32"],
+                       cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert f"finish=length -> {want}" in r.stdout and "stats:" in r.stdout
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(C.R))
+    r = subprocess.run([sys.executable, "-m", "servelab_b200", "--random-weights", str(cfg_path),
+                        "--prompt-ids", "1,2,3", "--max-tokens", "5", "--temperature", "0.8", "--seed", "3",
+                        "--ignore-eos", "--block-size", "4", "--num-blocks", "32"],
+                       cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "finish=length" in r.stdout, r.stderr[-2000:]
