@@ -164,6 +164,121 @@ def _daferax_rooflines(size, res, peaks) -> Dict[str, object]:
     return out
 
 
+# Zimupel: four layers -- linear attention with a decay and rotation, differential attention, linear
+# attention on activated q, k, v, differential attention that reads the second layer's cache -- each
+# followed by routed experts; the residual kept as `streams` copies.  A differential head has two
+# maps of `dim` elements and values of 2 dim, so half as many heads give the projections of a plain
+# attention.  Beside it the closest model the package has: Daferax with grouped-query attention in
+# every layer (keys = values = dim) and the same routed experts (no shared expert, no value mixing).
+# width, heads, kv heads, head size, experts, groups, kept groups, top, expert size, streams
+ZIMUPEL_SIZES = {
+    "lite-2048": (2048, 16, 4, 128, 32, 4, 2, 4, 1408, 4),
+    "small-1024": (1024, 8, 2, 64, 16, 2, 1, 2, 512, 2),
+}
+
+
+def zimupel_config(width, heads, kv, dim, experts, groups, keep, top, eff, streams, layers=LAYERS) -> dict:
+    mlp = {"kind": "moe", "expert": {"ff": eff},
+           "router": {"experts": experts, "groups": {"count": groups, "keep": keep}, "top": top}}
+    decay = [1.0 - 2.0 ** (-5 - 0.5 * i) for i in range(heads)]
+    ret = {"heads": heads, "dim": dim, "vdim": dim, "decay": decay, "rot": {"base": 1000000.0, "dims": dim}}
+    lig = {"heads": heads, "dim": dim, "vdim": dim, "decay": decay}
+    att = {"heads": heads // 2, "kv_heads": max(1, kv // 2), "dim": dim, "vdim": 2 * dim, "scale": dim ** -0.5,
+           "diff": 0.3}
+    kinds = [("retention", ret), ("attention", att), ("lightning", lig), ("attention", dict(att, kv_from=1))]
+    return {"architecture": "Zimupel", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5}, "streams": streams,
+            "logit_scale": 1.0, "logit_softcap": 30.0,
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(layers)]}
+
+
+def daferax_like_zimupel(width, heads, kv, dim, experts, groups, keep, top, eff, streams, layers=LAYERS) -> dict:
+    mlp = {"kind": "moe", "expert": {"ff": eff},
+           "router": {"experts": experts, "groups": {"count": groups, "keep": keep}, "scale": 1.0, "top": top}}
+    attn = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+            "rot": {"base": 1000000.0, "dims": dim}}
+    return {"architecture": "Daferax", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": attn, "mlp": mlp} for _ in range(layers)]}
+
+
+def _zimupel_rooflines(size, res, peaks) -> Dict[str, object]:
+    """Microseconds per launch and achieved fractions of the measured peaks for the kernels of the
+    Zimupel layers beside their Daferax counterparts, from the eager profiles.  Linear attention,
+    prefill: 4 T H D Dv flops (state update and output, the recurrence's own arithmetic, float32 on
+    CUDA cores) of the bf16 peak, beside the softmax attention's 2 (Dk + Dv) flops per visible pair
+    and head; decode: the state read and written once, of the copy bandwidth, beside the cached
+    rows the requests may see.  Elementwise kernels: the bytes they must move, of the copy
+    bandwidth."""
+    width, heads, kv, dim, experts, groups, keep, top, eff, streams = ZIMUPEL_SIZES[size]
+    out: Dict[str, object] = {}
+    zp, zd = res["zimupel"]["prefill_kernels_us"], res["zimupel"]["decode_b8_kernels_us"]
+    dp, dd = res["daferax"]["prefill_kernels_us"], res["daferax"]["decode_b8_kernels_us"]
+    n_lin, n_att = 2, 2
+    pairs = PROMPT * (PROMPT + 1) / 2
+
+    def hbm(nbytes, us):
+        return round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+
+    def tf(flops, us):
+        return round(flops / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
+
+    if zp.get("decay_attention"):
+        us = zp["decay_attention"] / n_lin
+        out["zimupel_linear_prefill_us_per_layer"] = round(us, 1)
+        out["zimupel_linear_prefill_bf16_frac"] = tf(4.0 * PROMPT * heads * dim * dim, us)
+    if zd.get("decay_attention"):
+        us = zd["decay_attention"] / n_lin
+        out["zimupel_linear_decode_us_per_layer"] = round(us, 2)
+        out["zimupel_linear_decode_hbm_frac"] = hbm(8 * 2 * heads * dim * dim * 4, us)
+    zatt = zp.get("attention_kv_mma") or zp.get("attention_kv_maps")
+    if zatt:
+        us = zatt / n_att
+        out["zimupel_differential_prefill_us_per_layer"] = round(us, 1)
+        out["zimupel_differential_prefill_bf16_frac"] = tf(pairs * (heads // 2) * 2 * 2 * (dim + 2 * dim), us)
+    zdatt = zd.get("attention_kv_mma") or zd.get("attention_kv_maps")
+    if zdatt:
+        us = zdatt / n_att
+        out["zimupel_differential_decode_us_per_layer"] = round(us, 2)
+        out["zimupel_differential_decode_hbm_frac"] = hbm(8 * CONTEXT * max(1, kv // 2) * 4 * dim * 2, us)
+    datt = (dp.get("prefill_attention_tc") or 0) + (dp.get("prefill_attention") or 0) + (dp.get("attention_kv_mma") or 0)
+    if datt:
+        us = datt / LAYERS
+        out["daferax_prefill_attention_us_per_layer"] = round(us, 1)
+        out["daferax_prefill_attention_bf16_frac"] = tf(pairs * heads * 4 * dim, us)
+    ddatt = dd.get("decode_attention") or dd.get("attention_kv_mma")
+    if ddatt:
+        us = ddatt / LAYERS
+        out["daferax_decode_attention_us_per_layer"] = round(us, 2)
+        out["daferax_decode_attention_hbm_frac"] = hbm(8 * CONTEXT * kv * 2 * dim * 2, us)
+    if zp.get("hyper_mix_norm"):
+        us = zp["hyper_mix_norm"] / (2 * LAYERS + 1)
+        out["zimupel_streams_norm_us"] = round(us, 2)
+        out["zimupel_streams_norm_hbm_frac"] = hbm(PROMPT * width * (8 * streams + 4), us)
+    if dp.get("ln_add_norm"):
+        us = dp["ln_add_norm"] / (2 * LAYERS + 1)
+        out["daferax_norm_us"], out["daferax_norm_hbm_frac"] = round(us, 2), hbm(PROMPT * 12 * width, us)
+    if zp.get("group_norm_gate"):
+        us = zp["group_norm_gate"] / LAYERS
+        out["zimupel_norm_gate_us"] = round(us, 2)
+        # linear layers: float32 row and gate in, row out; differential layers: two float32 maps in, row out
+        moved = PROMPT * heads * dim * ((4 + 2 + 2) * n_lin + (8 + 2) * n_att) / LAYERS
+        out["zimupel_norm_gate_hbm_frac"] = hbm(moved, us)
+    if zp.get("head_prep"):
+        us = zp["head_prep"] / n_att
+        out["zimupel_head_prep_us"] = round(us, 2)
+        out["zimupel_head_prep_hbm_frac"] = hbm(PROMPT * 4 * (heads * dim + 1.5 * kv * dim) , us)
+    if dp.get("head_prep"):
+        us = dp["head_prep"] / LAYERS
+        out["daferax_head_prep_us"] = round(us, 2)
+        out["daferax_head_prep_hbm_frac"] = hbm(PROMPT * 4 * (heads + 2 * kv) * dim, us)
+    for tag, a, b in (("prefill", zp, dp), ("decode_b8", zd, dd)):
+        for name in ("moe_route", "router_logits", "moe_gate_up", "moe_down", "moe_combine", "moe_plan", "gated_act",
+                     "embed_norm_streams"):
+            if a.get(name) or b.get(name):
+                out[f"{tag}_{name}_us_per_layer"] = {"zimupel": round((a.get(name) or 0) / LAYERS, 2),
+                                                     "daferax": round((b.get(name) or 0) / LAYERS, 2)}
+    return out
+
+
 def _measure(cfg: dict, note) -> Dict[str, object]:
     import torch
     from ..ops import kernels as K
@@ -285,6 +400,22 @@ def _kernel_rooflines(size, res: Dict[str, Dict[str, object]], peaks) -> Dict[st
 
 
 def run(peaks, note=lambda m: None, sizes=None, design: str = "dezelorn") -> Dict[str, object]:
+    if design == "zimupel":
+        result = {"compare": "zimupel vs daferax (grouped-query attention in every layer) at equal layer sizes",
+                  "layers": LAYERS, "prompt": PROMPT, "decode_context": CONTEXT, "vocab": VOCAB, "dtype": "bf16",
+                  "data": "synthetic: random weights, token ids uniform over the vocabulary",
+                  "peaks": peaks.get("source"), "sizes": {}}
+        for size in (sizes or ZIMUPEL_SIZES):
+            dims = ZIMUPEL_SIZES[size]
+            res = {}
+            for arch, make in (("zimupel", zimupel_config), ("daferax", daferax_like_zimupel)):
+                note(f"{size}: {arch}")
+                res[arch] = _measure(make(*dims), note)
+            res["kernels"] = _zimupel_rooflines(size, res, peaks)
+            res["dims"] = dict(zip(("width", "heads", "kv_heads", "head_dim", "experts", "groups", "keep", "top",
+                                    "expert_ff", "streams"), dims))
+            result["sizes"][size] = res
+        return result
     if design == "daferax":
         result = {"compare": "daferax vs qwen2 at equal layer sizes", "layers": LAYERS, "prompt": PROMPT,
                   "decode_context": CONTEXT, "window": WINDOW, "vocab": VOCAB, "dtype": "bf16",

@@ -18,6 +18,12 @@
 //
 // In a step of single tokens a tile holds the g query heads of one request that share the kv
 // head (all heads of a latent attention): the rows of the MMA are heads.
+//
+// Several attention maps a head (`maps`; not with `tied`): every query head and every kv head
+// carries `maps` query / key vectors side by side ([head][map][DK]; a cached key row is
+// [map][DK]), each map is an attention of its own over the kv head's one set of values, and a
+// block owns (tile, kv head, map).  The results go out map by map, [token][head][map][DV], as
+// float32 when `out_f32` is given, for the kernel that combines the maps.
 #include "mma_util.cuh"
 
 #ifndef SLB_KEY_DIM
@@ -46,7 +52,7 @@ __device__ int kv_attn_status_word = 0;
 __device__ __forceinline__ void load_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ kc,
                                           const bf16* __restrict__ vc, bool tied,
                                           const int* __restrict__ table, int k0, int kend, int kvh,
-                                          int Hkv, int ps, int num_pages) {
+                                          int Hkv, int ps, int num_pages, int ldk, int koff) {
     const int per_row = tied ? KCH : KCH + VCH;
     for (int idx = threadIdx.x; idx < BN * per_row; idx += NTHREADS) {
         const int r = idx / per_row, c = idx - r * per_row;
@@ -60,7 +66,7 @@ __device__ __forceinline__ void load_tile(bf16* Ks, bf16* Vs, const bf16* __rest
         }
         ok = ok && page >= 0;
         const size_t slot = ok ? ((size_t)page * Hkv + kvh) * ps + kp % ps : 0;
-        if (c < KCH) cp_async16(Ks + r * LDK + c * 8, kc + slot * DK + c * 8, ok);
+        if (c < KCH) cp_async16(Ks + r * LDK + c * 8, kc + slot * ldk + koff + c * 8, ok);
         else cp_async16(Vs + r * LDV + (c - KCH) * 8, vc + slot * DV + (c - KCH) * 8, ok);
     }
 }
@@ -71,7 +77,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
     const int* __restrict__ tile_row0, int H, int Hkv, int ps, int num_pages, float scale_log2,
     int window, const bf16* __restrict__ gate, int ldg, int splits, float* __restrict__ part_o,
-    float* __restrict__ part_ml) {
+    float* __restrict__ part_ml, int maps, float* __restrict__ out_f32) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDK]
@@ -79,8 +85,10 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     const int STAGE_ELEMS = stage_elems(tied != 0);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = blockIdx.x % Hkv;
-    const int tile = (int)(gridDim.x / Hkv) - 1 - (int)(blockIdx.x / Hkv);   // the longest first
+    const int units = Hkv * maps;
+    const int kvh = (blockIdx.x % units) / maps, map = (blockIdx.x % units) % maps;
+    const int ldk = maps * DK, koff = map * DK;
+    const int tile = (int)(gridDim.x / units) - 1 - (int)(blockIdx.x / units);   // the longest first
     const int s = tile_seq[tile];
     const int row0 = tile_row0[tile];
     const int g = H / Hkv;
@@ -97,7 +105,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         const bool ok = r < nrows;
         const int rho = row0 + (ok ? r : 0);
         const int tl = rho / g, hg = rho - tl * g;
-        cp_async16(Qs + r * LDK + c * 8, q + (size_t)(q0 + tl) * ldq + (size_t)(kvh * g + hg) * DK + c * 8, ok);
+        cp_async16(Qs + r * LDK + c * 8, q + (size_t)(q0 + tl) * ldq + (size_t)((kvh * g + hg) * maps + map) * DK + c * 8, ok);
     }
     cp_async_commit();
 
@@ -115,7 +123,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     }
 
     if (ntiles > 0)
-        load_tile(stage0, stage0 + BN * LDK, kc, vc, tied != 0, table, kbeg, kend, kvh, Hkv, ps, num_pages);
+        load_tile(stage0, stage0 + BN * LDK, kc, vc, tied != 0, table, kbeg, kend, kvh, Hkv, ps, num_pages, ldk, koff);
     cp_async_commit();
 
     const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
@@ -141,7 +149,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         if (t + 1 < ntiles) {
             bf16* Kn = stage0 + ((t + 1) & 1) * STAGE_ELEMS;
             load_tile(Kn, Kn + BN * LDK, kc, vc, tied != 0, table, kbeg + (t + 1) * BN, kend, kvh, Hkv, ps,
-                      num_pages);
+                      num_pages, ldk, koff);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -255,9 +263,9 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         if (row >= nrows) continue;
         const int rho = row0 + row;
         const int tl = rho / g, hg = rho - tl * g;
-        const int head = kvh * g + hg;
+        const int head = (kvh * g + hg) * maps + map;
         if (splits > 1) {
-            const size_t pi = ((size_t)(q0 + tl) * H + head) * splits + blockIdx.y;
+            const size_t pi = ((size_t)(q0 + tl) * H * maps + head) * splits + blockIdx.y;
             if (tig == 0) {
                 part_ml[2 * pi] = m[h];
                 part_ml[2 * pi + 1] = l[h];
@@ -273,6 +281,13 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
             const float z = __bfloat162float(gate[(size_t)(q0 + tl) * ldg + head]);
             inv *= 1.0f / (1.0f + __expf(-z));
         }
+        if (out_f32 != nullptr) {
+            float* dst = out_f32 + (size_t)(q0 + tl) * ldo + (size_t)head * DV + tig * 2;
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n)
+                *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+            continue;
+        }
         bf16* dst = out + (size_t)(q0 + tl) * ldo + (size_t)head * DV + tig * 2;
 #pragma unroll
         for (int n = 0; n < NT_O; ++n)
@@ -284,7 +299,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
 // head), a thread two neighbouring columns; the splits' weights are formed once per block.
 __global__ void __launch_bounds__(128) attention_kv_combine_kernel(
     const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits, bf16* __restrict__ out,
-    int ldo, int H, const bf16* __restrict__ gate, int ldg) {
+    int ldo, int H, const bf16* __restrict__ gate, int ldg, float* __restrict__ out_f32) {
     __shared__ float wgt[32];
     __shared__ float inv_s;
     pdl_wait();
@@ -314,7 +329,10 @@ __global__ void __launch_bounds__(128) attention_kv_combine_kernel(
             a0 += v.x * wgt[s];
             a1 += v.y * wgt[s];
         }
-        *reinterpret_cast<unsigned*>(out + t * ldo + (size_t)head * DV + c) = pack_bf16(a0 * inv_s, a1 * inv_s);
+        if (out_f32 != nullptr)
+            *reinterpret_cast<float2*>(out_f32 + t * ldo + (size_t)head * DV + c) = make_float2(a0 * inv_s, a1 * inv_s);
+        else
+            *reinterpret_cast<unsigned*>(out + t * ldo + (size_t)head * DV + c) = pack_bf16(a0 * inv_s, a1 * inv_s);
     }
 }
 
@@ -334,6 +352,35 @@ int slb_attention_kv_mma_status(int reset) {
     }
     return v;
 }
+static int launch_attention_kv_mma(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int tied, bf16* out,
+                                   float* out_f32, int ldo, const int* block_table, int max_pages, const int* cu_q,
+                                   const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
+                                   int H, int Hkv, int maps, int ps, int num_pages, float scale, int window,
+                                   const bf16* gate, int ldg, int splits, float* part_o, float* part_ml,
+                                   cudaStream_t st) {
+    // `splits` > 1 (steps of single tokens only: a tile is one token's heads): scratch part_o
+    // [tokens][H * maps][splits][DV] and part_ml [tokens][H * maps][splits][2], float32.
+    if (num_tiles <= 0) return 0;
+    if (splits < 1 || splits > 32 || (splits > 1 && (part_o == nullptr || part_ml == nullptr || H / Hkv > BM)))
+        return SLB_ERR_BAD_ARG;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || scale <= 0.f ||
+        (tied && DV > DK) || ldq % 8 != 0 || ldo % 2 != 0 || maps < 1 || (maps > 1 && tied))
+        return SLB_ERR_BAD_ARG;
+    if ((long long)num_tiles * Hkv * maps > 2147483647LL) return SLB_ERR_TOO_LARGE;
+    const size_t smem = ((size_t)BM * LDK + 2 * stage_elems(tied != 0)) * sizeof(bf16);
+    static unsigned long long configured = 0;
+    const int rc = slb_configure(&configured, attention_kv_mma_kernel,
+                                 ((size_t)BM * LDK + 2 * stage_elems(false)) * sizeof(bf16));
+    if (rc != 0) return rc;
+    const int e = slb_launch(attention_kv_mma_kernel, dim3(num_tiles * Hkv * maps, splits), dim3(NTHREADS), smem, st,
+                             q, ldq, kc, tied ? kc : vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len,
+                             tile_seq, tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window,
+                             gate, ldg, splits, part_o, part_ml, maps, out_f32);
+    if (e != 0 || splits == 1) return e;
+    // (one tile a token: num_tiles is the number of tokens)
+    return slb_launch(attention_kv_combine_kernel, dim3(num_tiles, H * maps), dim3(128), 0, st, (const float*)part_o,
+                      (const float*)part_ml, splits, out, ldo, H * maps, gate, ldg, out_f32);
+}
 // `tied`: the values are the first DV elements of the key rows (vc is ignored).
 int slb_attention_kv_mma_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int tied, bf16* out,
                               int ldo, const int* block_table, int max_pages, const int* cu_q,
@@ -341,27 +388,18 @@ int slb_attention_kv_mma_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
                               int H, int Hkv, int ps, int num_pages, float scale, int window,
                               const bf16* gate, int ldg, int splits, float* part_o, float* part_ml,
                               cudaStream_t st) {
-    // `splits` > 1 (steps of single tokens only: a tile is one token's heads): scratch part_o
-    // [tokens][H][splits][DV] and part_ml [tokens][H][splits][2], float32.
-    if (num_tiles <= 0) return 0;
-    if (splits < 1 || splits > 32 || (splits > 1 && (part_o == nullptr || part_ml == nullptr || H / Hkv > BM)))
-        return SLB_ERR_BAD_ARG;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || scale <= 0.f ||
-        (tied && DV > DK) || ldq % 8 != 0 || ldo % 2 != 0)
-        return SLB_ERR_BAD_ARG;
-    if ((long long)num_tiles * Hkv > 2147483647LL) return SLB_ERR_TOO_LARGE;
-    const size_t smem = ((size_t)BM * LDK + 2 * stage_elems(tied != 0)) * sizeof(bf16);
-    static unsigned long long configured = 0;
-    const int rc = slb_configure(&configured, attention_kv_mma_kernel,
-                                 ((size_t)BM * LDK + 2 * stage_elems(false)) * sizeof(bf16));
-    if (rc != 0) return rc;
-    const int e = slb_launch(attention_kv_mma_kernel, dim3(num_tiles * Hkv, splits), dim3(NTHREADS), smem, st, q,
-                             ldq, kc, tied ? kc : vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len,
-                             tile_seq, tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window,
-                             gate, ldg, splits, part_o, part_ml);
-    if (e != 0 || splits == 1) return e;
-    // (one tile a token: num_tiles is the number of tokens)
-    return slb_launch(attention_kv_combine_kernel, dim3(num_tiles, H), dim3(128), 0, st, (const float*)part_o,
-                      (const float*)part_ml, splits, out, ldo, H, gate, ldg);
+    return launch_attention_kv_mma(q, ldq, kc, vc, tied, out, nullptr, ldo, block_table, max_pages, cu_q, ctx_len,
+                                   tile_seq, tile_row0, num_tiles, H, Hkv, 1, ps, num_pages, scale, window, gate,
+                                   ldg, splits, part_o, part_ml, st);
+}
+// `maps` attention maps a head; float32 results [token][head][map][DV] with rows `ldo` floats apart
+int slb_attention_kv_mma_maps_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int maps, float* out,
+                                   int ldo, const int* block_table, int max_pages, const int* cu_q,
+                                   const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
+                                   int H, int Hkv, int ps, int num_pages, float scale, int window, int splits,
+                                   float* part_o, float* part_ml, cudaStream_t st) {
+    return launch_attention_kv_mma(q, ldq, kc, vc, 0, nullptr, out, ldo, block_table, max_pages, cu_q, ctx_len,
+                                   tile_seq, tile_row0, num_tiles, H, Hkv, maps, ps, num_pages, scale, window,
+                                   nullptr, 0, splits, part_o, part_ml, st);
 }
 }

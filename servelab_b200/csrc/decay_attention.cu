@@ -9,10 +9,11 @@
 // position * freq[i]); a factor on the keys.  Everything after the load is float32: activations,
 // angles, the state, the products and the sums.  No softmax, no denominator.
 //
-// Plain form (this kernel): a block owns (request, head, 32 value columns); thread (part, column)
-// keeps the state elements S[d][column] for d = part, part + 8, ... in registers, so a token costs
-// D / 8 multiply-adds for the state and as many for the output, and the eight parts of an output
-// are added through shared memory in a fixed order.  Tokens of the request's portion are taken in
+// A block owns (request, head, 32 value columns); thread (part, column) keeps the state elements
+// S[d][column] of its part's run of ceil(D / 8) neighbouring d in registers, so a token costs D / 8
+// multiply-adds for the state and as many for the output (q and k are read from shared memory four
+// at a time, the same address for a whole warp), and the eight parts of an output are added through
+// shared memory in a fixed order.  Tokens of the request's portion are taken in
 // order, eight at a time (their prepared q, k, v rows staged in shared memory).  The state is
 // read from the request's slot at the start and written back at the end, so a request can be cut
 // anywhere: the result of a token is bit-identical however the prompt is cut and whatever else is
@@ -70,9 +71,12 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS) decay_attention_kernel(const
     const int slot = a.state_slots[s];
     if (slot < 0 || slot >= a.num_slots) return;
     const int D = a.D, Dv = a.Dv;
-    float* qs = da_smem;                         // [DA_TT][D]
-    float* ks = qs + DA_TT * D;                  // [DA_TT][D]
-    float* vs = ks + DA_TT * D;                  // [DA_TT][DA_EV]
+    const int Dp = (D + DA_PARTS - 1) / DA_PARTS;          // state rows a part owns: d = p * Dp + i
+    const int Dpad = (Dp + 3) / 4 * 4;                     // a part's q and k in shared memory, 16-byte aligned
+    const int LD = DA_PARTS * Dpad;
+    float* qs = da_smem;                         // [DA_TT][LD]: element d at (d / Dp) * Dpad + d % Dp, zeros between
+    float* ks = qs + DA_TT * LD;                 // [DA_TT][LD]
+    float* vs = ks + DA_TT * LD;                 // [DA_TT][DA_EV]
     float* part = vs + DA_TT * DA_EV;            // [DA_TT][DA_PARTS][DA_EV]
     const int tid = threadIdx.x, p = tid >> 5, e = tid & 31;
     const int col = e0 + e;
@@ -83,18 +87,25 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS) decay_attention_kernel(const
     float st[DA_R];
 #pragma unroll
     for (int i = 0; i < DA_R; ++i) {
-        const int d = i * DA_PARTS + p;
-        st[i] = (live && d < D) ? srow[(size_t)d * Dv + col] : 0.f;
+        const int d = p * Dp + i;
+        st[i] = (live && i < Dp && d < D) ? srow[(size_t)d * Dv + col] : 0.f;
     }
     const T* proj = reinterpret_cast<const T*>(a.proj);
     for (int t0 = 0; t0 < qlen; t0 += DA_TT) {
         const int n = min(DA_TT, qlen - t0);
-        for (int idx = tid; idx < n * D; idx += DA_EV * DA_PARTS) {
-            const int j = idx / D, d = idx - j * D;
-            const T* row = proj + (size_t)(q0 + t0 + j) * a.ld;
-            const int pos = a.positions[q0 + t0 + j];
-            qs[j * D + d] = da_prepared(row + a.q_off + h * D, d, pos, a);
-            ks[j * D + d] = da_prepared(row + a.k_off + h * D, d, pos, a) * a.k_scale;
+        for (int idx = tid; idx < n * LD; idx += DA_EV * DA_PARTS) {
+            const int j = idx / LD, c = idx - j * LD;
+            const int pp = c / Dpad, i = c - pp * Dpad;
+            const int d = pp * Dp + i;
+            float qv = 0.f, kv = 0.f;                      // (the padding multiplies state elements that stay 0)
+            if (i < Dp && d < D) {
+                const T* row = proj + (size_t)(q0 + t0 + j) * a.ld;
+                const int pos = a.positions[q0 + t0 + j];
+                qv = da_prepared(row + a.q_off + h * D, d, pos, a);
+                kv = da_prepared(row + a.k_off + h * D, d, pos, a) * a.k_scale;
+            }
+            qs[idx] = qv;
+            ks[idx] = kv;
         }
         for (int idx = tid; idx < n * DA_EV; idx += DA_EV * DA_PARTS) {
             const int j = idx / DA_EV, c = e0 + (idx - j * DA_EV);
@@ -108,15 +119,21 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS) decay_attention_kernel(const
         __syncthreads();
         for (int j = 0; j < n; ++j) {
             const float v = vs[j * DA_EV + e];
-            const float* qj = qs + j * D;
-            const float* kj = ks + j * D;
+            const float4* qj = reinterpret_cast<const float4*>(qs + j * LD + p * Dpad);
+            const float4* kj = reinterpret_cast<const float4*>(ks + j * LD + p * Dpad);
             float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < DA_R; ++i) {
-                const int d = i * DA_PARTS + p;
-                if (d < D) {
-                    st[i] = fmaf(dec, st[i], kj[d] * v);
-                    acc = fmaf(st[i], qj[d], acc);
+            for (int i4 = 0; i4 < DA_R / 4; ++i4) {
+                if (i4 * 4 < Dp) {                         // (the same for every thread)
+                    const float4 k4 = kj[i4], q4 = qj[i4];
+                    st[4 * i4] = fmaf(dec, st[4 * i4], k4.x * v);
+                    acc = fmaf(st[4 * i4], q4.x, acc);
+                    st[4 * i4 + 1] = fmaf(dec, st[4 * i4 + 1], k4.y * v);
+                    acc = fmaf(st[4 * i4 + 1], q4.y, acc);
+                    st[4 * i4 + 2] = fmaf(dec, st[4 * i4 + 2], k4.z * v);
+                    acc = fmaf(st[4 * i4 + 2], q4.z, acc);
+                    st[4 * i4 + 3] = fmaf(dec, st[4 * i4 + 3], k4.w * v);
+                    acc = fmaf(st[4 * i4 + 3], q4.w, acc);
                 }
             }
             part[(j * DA_PARTS + p) * DA_EV + e] = acc;
@@ -136,8 +153,8 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS) decay_attention_kernel(const
     }
 #pragma unroll
     for (int i = 0; i < DA_R; ++i) {
-        const int d = i * DA_PARTS + p;
-        if (live && d < D) srow[(size_t)d * Dv + col] = st[i];
+        const int d = p * Dp + i;
+        if (live && i < Dp && d < D) srow[(size_t)d * Dv + col] = st[i];
     }
 }
 
@@ -150,7 +167,8 @@ static int launch_decay_attention(const DecayAttnArgs* a, int num_seqs, cudaStre
     if (a->D > DA_MAX_D || a->H > 65535) return SLB_ERR_TOO_LARGE;
     const int vz = (a->Dv + DA_EV - 1) / DA_EV;
     if (vz > 65535) return SLB_ERR_TOO_LARGE;
-    const size_t smem = ((size_t)2 * DA_TT * a->D + DA_TT * DA_EV + DA_TT * DA_PARTS * DA_EV) * sizeof(float);
+    const int dpad = ((a->D + DA_PARTS - 1) / DA_PARTS + 3) / 4 * 4;
+    const size_t smem = ((size_t)2 * DA_TT * DA_PARTS * dpad + DA_TT * DA_EV + DA_TT * DA_PARTS * DA_EV) * sizeof(float);
     return slb_launch(decay_attention_kernel<T>, dim3(num_seqs, a->H, vz), dim3(DA_EV * DA_PARTS), smem, st, *a);
 }
 

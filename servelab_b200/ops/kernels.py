@@ -1230,3 +1230,26 @@ def attention_kv_maps(ctx, q, k_cache, v_cache, out, block_table, num_heads: int
                ctx.cu_q.data_ptr(), ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n,
                num_heads, num_kv_heads, k_dim, v_dim, page_size, k_cache.shape[0], float(scale), int(window),
                _stream()), "attention_kv_maps")
+
+
+def attention_kv_mma_maps(ctx, q, k_cache, v_cache, out, block_table, num_heads: int, num_kv_heads: int,
+                          maps: int, k_dim: int, v_dim: int, page_size: int, scale: float, window: int = 0) -> None:
+    """The tensor-core kernel (bfloat16) with ``maps`` attention maps a head, layouts as
+    ``attention_kv_maps``; in a step of single tokens the keys of a request are split over several
+    blocks when the requests alone would not fill the device."""
+    lib = L.attention_kv(k_dim, v_dim)
+    rows = lib.slb_attention_kv_mma_tile_rows()
+    tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads, rows)
+    splits, part_o, part_ml = 1, None, None
+    if ctx.decode_only and attention_kv_split and num_heads // num_kv_heads <= rows:
+        splits = attention_kv_splits(ctx.num_seqs, num_kv_heads * maps, ctx.split_hint_len, window,
+                                     max_splits=lib.slb_attention_kv_mma_max_splits())
+        if splits > 1:
+            T = q.shape[0]
+            part_o = torch.empty((T, num_heads * maps, splits, v_dim), dtype=_F32, device=q.device)
+            part_ml = torch.empty((T, num_heads * maps, splits, 2), dtype=_F32, device=q.device)
+    L.check(lib.slb_attention_kv_mma_maps_bf16(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), maps, out.data_ptr(), out.stride(0),
+        block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_len.data_ptr(),
+        tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads, page_size, k_cache.shape[0],
+        float(scale), int(window), splits, _p(part_o), _p(part_ml), _stream()), "attention_kv_mma")

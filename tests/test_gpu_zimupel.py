@@ -324,24 +324,52 @@ def _maps_case(seed, Hq, G, D, Dv, ctxs, qlens, ps, dtype, spike=None):
     return torch.cat(qs), kc, vc, torch.cat(wants), entries
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(4, 2, 16, 8, 8), (3, 3, 10, 6, 4), (4, 1, 64, 128, 16), (2, 1, 48, 96, 16)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, "plain twin"])
+@pytest.mark.parametrize("shape", [(4, 2, 16, 8, 8), (3, 3, 10, 6, 4), (4, 1, 64, 128, 16), (2, 1, 48, 96, 16),
+                                   (6, 3, 32, 16, 8)])
 @pytest.mark.parametrize("spike", [None, 0, 1, 33, 290])
-def test_attention_with_two_maps(dtype, shape, spike):
+def test_attention_with_two_maps(dtype, shape, spike, monkeypatch):
     """Portions of unequal requests and single tokens in one batch; a key made dominant in the second
-    map only at the query itself, one back, across page and tile borders and 290 tokens back."""
+    map only at the query itself, one back, across page and tile borders and 290 tokens back.
+    bfloat16: the tensor-core kernel where the sizes are multiples of 16, and the plain kernel."""
     from servelab_b200.ops import attention as A
+    if dtype == "plain twin":
+        monkeypatch.setattr(A, "use_kv_fast", False)
+        dtype = torch.bfloat16
     Hq, G, D, Dv, ps = shape
     ctxs, qlens = [300, 41, 1, 333, 64], [9, 41, 1, 1, 33]
     q, kc, vc, want, entries = _maps_case(17 + D, Hq, G, D, Dv, ctxs, qlens, ps, dtype, spike)
     ctx = _ctx(entries)
     out = torch.empty(q.shape[0], Hq * 2 * Dv, dtype=torch.float32, device=DEV)
+    A.prepare_maps_attention(D, Dv, dtype)
     A.maps_attention(ctx, q.to(DEV), kc.to(DEV), vc.to(DEV), out, ctx.block_tables[0], Hq, G, 2, D, Dv, ps, 0.3, 0)
     tol = 3e-5 if dtype == torch.float32 else 3e-2
     assert (out.cpu().double() - want).abs().max() < tol * max(1.0, float(want.abs().max()))
     if spike is not None:                # the second map of the single token after 332 others found its key
         row = sum(qlens[:3])
         assert out.view(-1, Hq, 2, Dv)[row, 0, 1].min() > 9.9 and out.view(-1, Hq, 2, Dv)[row, 0, 0].max() < 9
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(4, 1, 64, 128, 16), (4, 2, 48, 96, 32), (3, 3, 10, 6, 4)])
+def test_attention_with_two_maps_single_tokens_at_long_contexts(dtype, shape):
+    """A step of single tokens only (few requests, long contexts: the tensor-core kernel splits the
+    keys over blocks), with a dominant key 900 tokens back in the second map."""
+    from servelab_b200.ops import attention as A
+    from servelab_b200.ops import kernels as K
+    Hq, G, D, Dv, ps = shape
+    ctxs, qlens = [1400, 901, 1000], [1, 1, 1]
+    q, kc, vc, want, entries = _maps_case(5 + D, Hq, G, D, Dv, ctxs, qlens, ps, dtype, 900)
+    ctx = _ctx(entries)
+    assert ctx.decode_only
+    if dtype == torch.bfloat16 and D % 16 == 0:
+        assert K.attention_kv_splits(3, G * 2, 1400, 0) > 1
+    out = torch.empty(3, Hq * 2 * Dv, dtype=torch.float32, device=DEV)
+    A.prepare_maps_attention(D, Dv, dtype)
+    A.maps_attention(ctx, q.to(DEV), kc.to(DEV), vc.to(DEV), out, ctx.block_tables[0], Hq, G, 2, D, Dv, ps, 0.3, 0)
+    tol = 3e-5 if dtype == torch.float32 else 3e-2
+    assert (out.cpu().double() - want).abs().max() < tol * max(1.0, float(want.abs().max()))
+    assert out.view(3, Hq, 2, Dv)[:, :, 1].min() > 9.9
 
 
 # ------------------------------------------------------------ whole models
