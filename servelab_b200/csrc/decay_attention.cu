@@ -19,45 +19,13 @@
 // anywhere: the result of a token is bit-identical however the prompt is cut and whatever else is
 // in the batch.  Steps of single tokens run the same kernel: then it is one read and one write of
 // the state.
-#include "common.cuh"
+#include "decay_attention.cuh"
 
 #define DA_EV 32
 #define DA_PARTS 8
 #define DA_TT 8
 #define DA_MAX_D 256
 #define DA_R (DA_MAX_D / DA_PARTS)
-
-struct DecayAttnArgs {
-    const void* proj; int ld;
-    int q_off, k_off, v_off;
-    int H, D, Dv;
-    int act;                       // 0: none; 1: SiLU on q, k and v
-    const float* freq; int rot_dims;
-    float k_scale;
-    const float* decay;            // [H]
-    const int* positions; const int* cu_q; const int* state_slots;
-    float* state; int num_slots;   // [num_slots][H][D][Dv]
-    float* out; int ldo;           // [T][H * Dv] float32
-};
-
-__device__ __forceinline__ float da_silu(float z) { return z / (1.0f + expf(-z)); }
-
-// element d of a query or key head of token `row` (a pointer to the head's first element)
-template <typename T>
-__device__ __forceinline__ float da_prepared(const T* head, int d, int pos, const DecayAttnArgs& a) {
-    float x = to_float(head[d]);
-    if (a.act == 1) x = da_silu(x);
-    if (d < a.rot_dims) {
-        const int half = a.rot_dims >> 1;
-        const int i = d < half ? d : d - half;
-        float other = to_float(head[d < half ? d + half : d - half]);
-        if (a.act == 1) other = da_silu(other);
-        float sn, cs;
-        sincosf((float)pos * a.freq[i], &sn, &cs);
-        x = d < half ? x * cs - other * sn : x * cs + other * sn;
-    }
-    return x;
-}
 
 template <typename T>
 __global__ void __launch_bounds__(DA_EV * DA_PARTS) decay_attention_kernel(const DecayAttnArgs a) {

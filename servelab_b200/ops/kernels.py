@@ -1194,6 +1194,20 @@ class _DecayAttnArgs(_ct.Structure):
     ]
 
 
+class _DecayChunkArgs(_ct.Structure):
+    _fields_ = [("a", _DecayAttnArgs), ("tile_seq", _ct.c_void_p), ("tile_row0", _ct.c_void_p),
+                ("num_tiles", _ct.c_int), ("work", _ct.c_void_p)]
+
+
+# Steps that bring portions of prompts in bfloat16 take the chunked tensor-core kernels when the
+# step has at least this many tokens a request (shorter portions: the recurrent kernel, which is
+# also the float32 path and the one for steps of single tokens).
+decay_attention_chunked = True
+decay_attention_chunk_min_tokens = 16
+# operands of the chunked kernels' products as two bfloat16 numbers each (three MMAs a product)
+decay_attention_split = True
+
+
 def decay_attention_max_dim() -> int:
     return L.core().slb_decay_attention_max_dim()
 
@@ -1215,6 +1229,19 @@ def decay_attention(proj: torch.Tensor, ctx, state: torch.Tensor, decay: torch.T
     a.positions, a.cu_q, a.state_slots = ctx.positions.data_ptr(), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr()
     a.state, a.num_slots = state.data_ptr(), state.shape[0]
     a.out, a.ldo = out.data_ptr(), out.stride(0)
+    if (decay_attention_chunked and proj.dtype == torch.bfloat16 and not ctx.decode_only
+            and head_dim <= L.core().slb_decay_chunk_max_dim()
+            and ctx.num_tokens >= decay_attention_chunk_min_tokens * ctx.num_seqs):
+        # portions of prompts: the chunked form on the tensor cores
+        tile_seq, tile_row0, n = ctx.attention_tiles(1, L.core().slb_decay_chunk_tokens())
+        c = _DecayChunkArgs()
+        c.a = a
+        c.tile_seq, c.tile_row0, c.num_tiles = tile_seq.data_ptr(), tile_row0.data_ptr(), n
+        work = torch.empty((max(n, 1), num_heads, head_dim, value_dim), dtype=torch.float32, device=proj.device)
+        c.work = work.data_ptr()
+        L.check(L.core().slb_decay_chunk_bf16(_ct.byref(c), ctx.num_seqs, int(decay_attention_split), _stream()),
+                "decay_attention (chunked)")
+        return
     fn = getattr(L.core(), "slb_decay_attention_" + _suffix(proj.dtype))
     L.check(fn(_ct.byref(a), ctx.num_seqs, _stream()), "decay_attention")
 

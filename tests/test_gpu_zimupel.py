@@ -204,10 +204,21 @@ def _decay_want(proj, decay, Hh, D, Dv, lens, act, rot, key_scale):
     return torch.cat(out)
 
 
-def _run_decay(proj, decay, state, Hh, D, Dv, pieces, act, rot, key_scale):
+def _run_decay(proj, decay, state, Hh, D, Dv, pieces, act, rot, key_scale, chunked=False, split=True):
     """``pieces``: per step a list of (request, tokens); requests are laid out one after the other in
-    ``proj`` and own the state slot of their number.  Returns the outputs in ``proj``'s order."""
+    ``proj`` and own the state slot of their number.  Returns the outputs in ``proj``'s order.
+    ``chunked``: bfloat16 steps with portions take the chunked tensor-core kernels (else every step
+    takes the recurrent kernel)."""
     from servelab_b200.ops import kernels as K
+    before = K.decay_attention_chunked, K.decay_attention_split
+    K.decay_attention_chunked, K.decay_attention_split = chunked, split
+    try:
+        return _run_decay_steps(K, proj, decay, state, Hh, D, Dv, pieces, act, rot, key_scale)
+    finally:
+        K.decay_attention_chunked, K.decay_attention_split = before
+
+
+def _run_decay_steps(K, proj, decay, state, Hh, D, Dv, pieces, act, rot, key_scale):
     lens = {}
     for step in pieces:
         for r, n in step:
@@ -282,6 +293,59 @@ def test_decay_attention_keeps_a_key_from_far_back():
     out = _run_decay(proj, decay, state, Hh, D, Dv, [[(0, 1000)], [(0, 599)], [(0, 1)]], None, None, 1.0)
     want = _decay_want(proj, decay, Hh, D, Dv, [n], None, None, 1.0)
     assert (out - want).abs().max() < 5e-6 * float(want.abs().max())       # (float32 sums of 1,600 terms)
+    assert out[n - 1, :Dv].min() > 70 and out[n - 1, Dv:].abs().max() < 1.0
+
+
+@pytest.mark.parametrize("split", [True, False])
+@pytest.mark.parametrize("shape", [(3, 8, 12, None, None), (2, 16, 8, None, (500.0, 8)), (1, 24, 40, "silu", None),
+                                   (2, 64, 64, None, (10000.0, 64)), (3, 10, 6, "silu", (900.0, 4)),
+                                   (2, 128, 96, "silu", None), (1, 128, 130, None, (1e6, 64)),
+                                   (2, 48, 64, None, (300.0, 48))])
+def test_decay_attention_in_chunks_on_the_tensor_cores(shape, split):
+    """The chunked kernels against the closed form: requests of unequal length (shorter than a
+    chunk, a chunk exactly, a chunk and one token, several chunks) in one batch; then the same in
+    portions whose cuts fall inside chunks, with single tokens between them (those steps take the
+    recurrent kernel), the state carried in slots.  With operands in two bfloat16 numbers the
+    result is as close to the closed form as float32 sums are; with one, as bfloat16 operands."""
+    Hh, D, Dv, act, rot = shape
+    lens = [37, 5, 64, 65, 200, 129]
+    proj, decay = _decay_case(D + 3 * Dv, Hh, D, Dv, lens, torch.bfloat16)
+    ks = D ** -0.5
+    want = _decay_want(proj, decay, Hh, D, Dv, lens, act, rot, ks)
+    tol = (3e-5 if split else 2e-2) * max(1.0, float(want.abs().max()))
+    state = torch.full((8, Hh, D, Dv), 7.0, dtype=torch.float32, device=DEV)
+    state[:6] = 0
+    whole = _run_decay(proj, decay, state, Hh, D, Dv, [[(r, n) for r, n in enumerate(lens)]], act, rot, ks,
+                       chunked=True, split=split)
+    assert (whole - want).abs().max() < tol
+    assert torch.all(state[6:] == 7.0)
+    final = state[:6].clone()
+    state[:6] = 0
+    twin = _run_decay(proj, decay, state, Hh, D, Dv, [[(r, n) for r, n in enumerate(lens)]], act, rot, ks)
+    assert (twin - want).abs().max() < 3e-5 * max(1.0, float(want.abs().max()))
+    assert (state[:6] - final).abs().max() < (3e-5 if split else 2e-2) * max(1.0, float(final.abs().max()))
+    state[:6] = 0
+    pieces = [[(0, 30), (2, 63), (4, 100), (5, 2)], [(0, 1), (4, 1)], [(0, 6), (1, 5), (2, 1), (3, 65), (4, 99), (5, 127)]]
+    cut = _run_decay(proj, decay, state, Hh, D, Dv, pieces, act, rot, ks, chunked=True, split=split)
+    assert (cut - want).abs().max() < tol
+    assert (state[:6] - final).abs().max() < (3e-5 if split else 2e-2) * max(1.0, float(final.abs().max()))
+
+
+def test_decay_attention_in_chunks_keeps_a_key_from_far_back():
+    """As the test of the recurrent kernel: a key 1,500 tokens and two dozen chunks back."""
+    Hh, D, Dv, n = 2, 16, 8, 1600
+    g = torch.Generator().manual_seed(2)
+    proj = torch.randn(n, 2 * Hh * D + Hh * Dv, generator=g) * 0.01
+    for h in range(Hh):
+        proj[100, Hh * D + h * D] = 5.0
+        proj[100, 2 * Hh * D + h * Dv:2 * Hh * D + (h + 1) * Dv] = 3.0
+        proj[n - 1, h * D] = 5.0
+    proj = proj.to(torch.bfloat16)
+    decay = torch.tensor([1.0, 0.9])
+    state = torch.zeros(1, Hh, D, Dv, dtype=torch.float32, device=DEV)
+    out = _run_decay(proj, decay, state, Hh, D, Dv, [[(0, 1000)], [(0, 599)], [(0, 1)]], None, None, 1.0, chunked=True)
+    want = _decay_want(proj, decay, Hh, D, Dv, [n], None, None, 1.0)
+    assert (out - want).abs().max() < 2e-5 * float(want.abs().max())
     assert out[n - 1, :Dv].min() > 70 and out[n - 1, Dv:].abs().max() < 1.0
 
 
