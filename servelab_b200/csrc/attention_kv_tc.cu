@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(THREADS, TMEM_COLS == 512 ? 1 : 2) attention_k
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_q,
     const int* __restrict__ ctx_len, const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
     int H, int Hkv, int ps, int box_rows, float scale_log2, int window, int* __restrict__ status, int tied,
-    const bf16* __restrict__ gate, int ldg) {
+    const bf16* __restrict__ gate, int ldg, int maps, float* __restrict__ out32, int ldo32) {
     extern __shared__ __align__(1024) unsigned char smem[];
     // All barriers come in pairs indexed by tile parity.  s_full[b]: Q.K^T of a tile is done
     // (its scores are ready and its keys may be replaced); pv_done[b]: its P.V is done (its
@@ -196,8 +196,12 @@ __global__ void __launch_bounds__(THREADS, TMEM_COLS == 512 ? 1 : 2) attention_k
     // Blocks are handed out in the order of their linear index: tile by tile from the last
     // (most keys) to the first, all kv heads of a tile together, so that no head's long
     // tiles start late.
-    const int kvh = blockIdx.x % Hkv;
-    const int tile = (int)(gridDim.x / Hkv) - 1 - (int)(blockIdx.x / Hkv);
+    // With several attention maps a head (`maps` > 1) a block takes one map of a kv head: query
+    // head h's map m sits at column (h * maps + m) * DK of q, a cached key row holds the kv head's
+    // maps side by side, the values are shared, and the result goes to out32 (float32, laid out as q).
+    const int units = Hkv * maps;
+    const int kvh = (int)(blockIdx.x % units) / maps, amap = (int)(blockIdx.x % units) % maps;
+    const int tile = (int)(gridDim.x / units) - 1 - (int)(blockIdx.x / units);
     const int s = tile_seq[tile];
     const int row0 = tile_row0[tile];
     const int g = H / Hkv;
@@ -245,7 +249,7 @@ __global__ void __launch_bounds__(THREADS, TMEM_COLS == 512 ? 1 : 2) attention_k
         unsigned char* qs = smem + OFF_Q;
         if (r < nrows) {
             const int tl = r / g, hg = r - tl * g;
-            const bf16* src = q + (size_t)(q0 + tok0 + tl) * ldq + (size_t)(kvh * g + hg) * DK;
+            const bf16* src = q + (size_t)(q0 + tok0 + tl) * ldq + (size_t)((kvh * g + hg) * maps + amap) * DK;
 #pragma unroll
             for (int c = 0; c < DK / 8; ++c) {
                 const uint4 v = *reinterpret_cast<const uint4*>(src + c * 8);
@@ -310,7 +314,7 @@ __global__ void __launch_bounds__(THREADS, TMEM_COLS == 512 ? 1 : 2) attention_k
             if (row >= 0) {
                 for (int p = 0; p < panels; ++p)
                     tma_load_2d(ring + st * tile_bytes + p * KV_PANEL_BYTES + lane * box_rows * 128, map,
-                                &full[st], p * 64, row);
+                                &full[st], p * 64 + (keys ? amap * DK : 0), row);
             }
             row = next_row;
         }
@@ -449,12 +453,19 @@ __global__ void __launch_bounds__(THREADS, TMEM_COLS == 512 ? 1 : 2) attention_k
         if (gate != nullptr && r < nrows)
             inv *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)(q0 + tok0 + tl) * ldg + kvh * g + hg])));
         bf16* dst = out + (size_t)(q0 + tok0 + tl) * ldo + (size_t)(kvh * g + hg) * DV;
+        float* dst32 = out32 + (size_t)(q0 + tok0 + tl) * ldo32 + (size_t)((kvh * g + hg) * maps + amap) * DV;
 #pragma unroll
         for (int c0 = 0; c0 < DV; c0 += 32) {
             uint32_t ov[32];
             tmem_ld32(tmem + lane_base + O_COL + c0, ov);            // warp-wide: every lane takes part
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (ok && r < nrows) {
+            if (ok && r < nrows && out32 != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4*>(dst32 + c0 + i) =
+                        make_float4(__uint_as_float(ov[i]) * inv, __uint_as_float(ov[i + 1]) * inv,
+                                    __uint_as_float(ov[i + 2]) * inv, __uint_as_float(ov[i + 3]) * inv);
+            } else if (ok && r < nrows) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
                     uint4 v;
@@ -488,27 +499,34 @@ int slb_attention_kv_tc_supported(int ps, int group, int tied) {
 // query rows per tile for a group of g query heads (whole tokens per tile)
 int slb_attention_kv_tc_tile_rows(int group) { return group >= 1 && group <= BM ? (BM / group) * group : 0; }
 
-// num_pages: pages in k_cache ([num_pages][Hkv][ps][DK]) and v_cache ([..][DV]; ignored with `tied`).
-int slb_attention_kv_tc_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int tied, bf16* out, int ldo,
-                             const int* block_table, int max_pages, const int* cu_q, const int* ctx_len,
-                             const int* tile_seq, const int* tile_row0, int num_tiles, int H, int Hkv, int ps,
-                             int num_pages, float scale, int window, const bf16* gate, int ldg,
-                             cudaStream_t st) {
+}  // extern "C"
+
+static int launch_attention_kv_tc(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int tied, bf16* out, int ldo,
+                                  const int* block_table, int max_pages, const int* cu_q, const int* ctx_len,
+                                  const int* tile_seq, const int* tile_row0, int num_tiles, int H, int Hkv, int ps,
+                                  int num_pages, float scale, int window, const bf16* gate, int ldg, int maps,
+                                  float* out32, int ldo32, cudaStream_t st) {
     if (num_tiles <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f))
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f) || maps < 1 ||
+        maps > 64)
         return SLB_ERR_BAD_ARG;
     if (!slb_attention_kv_tc_supported(ps, H / Hkv, tied)) return SLB_ERR_BAD_ARG;
     if (tied) vc = kc;
-    if (ldq % 8 || ldo % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) % 16)
+    if (out32 != nullptr) {
+        if (ldo32 % 4 || (uintptr_t)out32 % 16) return SLB_ERR_BAD_ARG;
+    } else if (maps != 1 || ldo % 8 || (uintptr_t)out % 16) {
         return SLB_ERR_BAD_ARG;
-    if ((long long)num_tiles * Hkv > 0x7fffffffll) return SLB_ERR_TOO_LARGE;
+    }
+    if (maps > 1 && (tied || gate != nullptr)) return SLB_ERR_BAD_ARG;
+    if (ldq % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) % 16) return SLB_ERR_BAD_ARG;
+    if ((long long)num_tiles * Hkv * maps > 0x7fffffffll) return SLB_ERR_TOO_LARGE;
     const int box_rows = ps < BN ? ps : BN;
     CUtensorMap map_k, map_v;
     const long long rows = (long long)num_pages * Hkv * ps;
     if (rows > 0x7fffffffll) return SLB_ERR_TOO_LARGE;    // box coordinates are 32-bit
     // (a block-table entry outside [0, num_pages) names rows outside the tensor map: the copy
     // reads zeros there, never memory outside the cache)
-    int rc = slb_tma::make_rows_map(&map_k, kc, DK, rows, box_rows);
+    int rc = slb_tma::make_rows_map(&map_k, kc, maps * DK, rows, box_rows);
     if (rc != 0) return rc;
     rc = tied ? slb_tma::make_rows_map(&map_v, kc, DK, rows, box_rows)
               : slb_tma::make_rows_map(&map_v, vc, DV, rows, box_rows);
@@ -520,11 +538,36 @@ int slb_attention_kv_tc_bf16(const bf16* q, int ldq, const bf16* kc, const bf16*
     int* status = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_attn_status);
     if (e != cudaSuccess) return (int)e;
-    return slb_launch(attention_kv_tc_kernel, dim3((unsigned)num_tiles * Hkv), dim3(THREADS), smem, st, q, ldq,
+    return slb_launch(attention_kv_tc_kernel, dim3((unsigned)num_tiles * Hkv * maps), dim3(THREADS), smem, st, q, ldq,
                       map_k, map_v, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq, tile_row0, H, Hkv,
-                      ps, box_rows, scale * 1.4426950408889634f, window, status, tied, gate, ldg);
+                      ps, box_rows, scale * 1.4426950408889634f, window, status, tied, gate, ldg, maps, out32, ldo32);
 }
 
+extern "C" {
+// num_pages: pages in k_cache ([num_pages][Hkv][ps][DK]) and v_cache ([..][DV]; ignored with `tied`).
+int slb_attention_kv_tc_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int tied, bf16* out, int ldo,
+                             const int* block_table, int max_pages, const int* cu_q, const int* ctx_len,
+                             const int* tile_seq, const int* tile_row0, int num_tiles, int H, int Hkv, int ps,
+                             int num_pages, float scale, int window, const bf16* gate, int ldg,
+                             cudaStream_t st) {
+    return launch_attention_kv_tc(q, ldq, kc, vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
+                                  tile_row0, num_tiles, H, Hkv, ps, num_pages, scale, window, gate, ldg, 1, nullptr,
+                                  0, st);
+}
+// `maps` attention maps a head: q [T][H][maps][DK], k_cache [num_pages][Hkv][ps][maps * DK], one set
+// of values a kv head, float32 results per map out32 [T][H][maps][DV].
+int slb_attention_kv_tc_maps_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, float* out32, int ldo32,
+                                  const int* block_table, int max_pages, const int* cu_q, const int* ctx_len,
+                                  const int* tile_seq, const int* tile_row0, int num_tiles, int H, int Hkv, int maps,
+                                  int ps, int num_pages, float scale, int window, cudaStream_t st) {
+    if (out32 == nullptr) return SLB_ERR_BAD_ARG;
+    return launch_attention_kv_tc(q, ldq, kc, vc, 0, nullptr, 0, block_table, max_pages, cu_q, ctx_len, tile_seq,
+                                  tile_row0, num_tiles, H, Hkv, ps, num_pages, scale, window, nullptr, 0, maps, out32,
+                                  ldo32, st);
+}
+}
+
+extern "C" {
 // copies the twelve ints that say where waits gave up last (see tc_attn_where)
 int slb_attention_kv_tc_where(int* out12) {
     return (int)cudaMemcpyFromSymbol(out12, tc_attn_where, 12 * sizeof(int));
@@ -548,6 +591,11 @@ int slb_attention_kv_tc_supported(int, int, int) { return 0; }
 int slb_attention_kv_tc_bf16(const bf16*, int, const bf16*, const bf16*, int, bf16*, int, const int*, int, const int*,
                              const int*, const int*, const int*, int, int, int, int, int, float, int, const bf16*,
                              int, cudaStream_t) {
+    return SLB_ERR_BAD_ARG;
+}
+int slb_attention_kv_tc_maps_bf16(const bf16*, int, const bf16*, const bf16*, float*, int, const int*, int, const int*,
+                                  const int*, const int*, const int*, int, int, int, int, int, int, float, int,
+                                  cudaStream_t) {
     return SLB_ERR_BAD_ARG;
 }
 int slb_attention_kv_tc_tile_rows(int) { return 0; }

@@ -11,7 +11,7 @@
 //
 //   1. local sums   a block per (chunk, head, 64 value columns): L = sum_j g^(n-1-j) k_j v_j^T, float32
 //                   into a work buffer [chunks, H, D, Dv];
-//   2. scan         a thread per four state elements of a (request, head): walks the request's chunks
+//   2. scan         a thread per state element of a (request, head): walks the request's chunks
 //                   in order, S <- g^n S + L in float32, leaves in the work buffer the state that ENTERS
 //                   each chunk, and the final state in the request's slot;
 //   3. outputs      a block per (chunk, head, 64 value columns): the formula for o_i above.
@@ -30,11 +30,12 @@
 using namespace slb_mma;
 
 #define DC_CHUNK 64
-#define DC_THREADS 128
+#define DC_THREADS 256
 #define DC_PAD 8                   // bf16 elements added to every shared row (ldmatrix without bank conflicts)
 #define DC_MAX_D 128
 #define DC_EV 64                   // value columns a block
 #define DC_LDV (DC_EV + DC_PAD)
+#define DC_SCAN_BATCH 16
 
 struct DecayChunkArgs {
     DecayAttnArgs a;
@@ -70,44 +71,111 @@ __device__ __forceinline__ void dc_mma(float (&c)[4], const unsigned (&ah)[4], c
     mma_bf16(c, ah, bh0, bh1);
 }
 
-// Prepared q and / or k of the chunk's n tokens into shared rows of `ld` elements (zeroed before);
-// the lo halves sit `lo_off` elements behind the hi ones.
+// eight neighbours at index idx (a multiple of 8; the arrays are 16-byte aligned)
 template <bool SPLIT>
+__device__ __forceinline__ void dc_put8(bf16* hi, int lo_off, int idx, const float (&x)[8]) {
+    unsigned h[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        h[e] = pack_bf16(x[2 * e], x[2 * e + 1]);
+        if (SPLIT) {
+            const __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162*>(&h[e]);
+            l[e] = pack_bf16(x[2 * e] - __low2float(hv), x[2 * e + 1] - __high2float(hv));
+        }
+    }
+    *reinterpret_cast<uint4*>(hi + idx) = make_uint4(h[0], h[1], h[2], h[3]);
+    if (SPLIT) *reinterpret_cast<uint4*>(hi + lo_off + idx) = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+__device__ __forceinline__ void dc_load8(float (&x)[8], const bf16* p, bool act) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+        x[2 * e] = act ? da_silu(f.x) : f.x;
+        x[2 * e + 1] = act ? da_silu(f.y) : f.y;
+    }
+}
+
+// Prepared q and / or k of the chunk's n tokens into shared rows of `ld` elements (rows from n on
+// and columns from D on are zeroed by the caller); the lo halves sit `lo_off` elements behind the
+// hi ones.  Eight elements a load where the sizes and offsets are multiples of 8 (and the rotated
+// part of 16), else one.
+template <bool SPLIT, bool WITH_Q>
 __device__ __forceinline__ void dc_stage_qk(bf16* qs, bf16* ks, int ld, int lo_off, const bf16* proj, int tok0, int n,
                                             int h, const DecayAttnArgs& a) {
     const int D = a.D, half = a.rot_dims >> 1, rest = D - a.rot_dims;
     const bool act = a.act == 1;
+    const bool wide = ((a.ld | a.q_off | a.k_off | D | half) & 7) == 0 && (reinterpret_cast<size_t>(proj) & 15) == 0;
+    if (wide) {
+        const int hv = half >> 3, rv = rest >> 3;
+        for (int idx = threadIdx.x; idx < n * hv; idx += DC_THREADS) {
+            const int j = idx / hv, i = (idx - j * hv) << 3;
+            const bf16* row = proj + (size_t)(tok0 + j) * a.ld + h * D + i;
+            float qu[8], qv[8], ku[8], kv[8], sn[8], cs[8], x[8], y[8];
+            if (WITH_Q) { dc_load8(qu, row + a.q_off, act); dc_load8(qv, row + a.q_off + half, act); }
+            dc_load8(ku, row + a.k_off, act);
+            dc_load8(kv, row + a.k_off + half, act);
+            const float pos = (float)a.positions[tok0 + j];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sincosf(pos * a.freq[i + e], &sn[e], &cs[e]);
+            if (WITH_Q) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { x[e] = qu[e] * cs[e] - qv[e] * sn[e]; y[e] = qv[e] * cs[e] + qu[e] * sn[e]; }
+                dc_put8<SPLIT>(qs, lo_off, j * ld + i, x);
+                dc_put8<SPLIT>(qs, lo_off, j * ld + i + half, y);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                x[e] = (ku[e] * cs[e] - kv[e] * sn[e]) * a.k_scale;
+                y[e] = (kv[e] * cs[e] + ku[e] * sn[e]) * a.k_scale;
+            }
+            dc_put8<SPLIT>(ks, lo_off, j * ld + i, x);
+            dc_put8<SPLIT>(ks, lo_off, j * ld + i + half, y);
+        }
+        for (int idx = threadIdx.x; idx < n * rv; idx += DC_THREADS) {
+            const int j = idx / rv, d = a.rot_dims + ((idx - j * rv) << 3);
+            const bf16* row = proj + (size_t)(tok0 + j) * a.ld + h * D + d;
+            float x[8];
+            if (WITH_Q) {
+                dc_load8(x, row + a.q_off, act);
+                dc_put8<SPLIT>(qs, lo_off, j * ld + d, x);
+            }
+            dc_load8(x, row + a.k_off, act);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[e] *= a.k_scale;
+            dc_put8<SPLIT>(ks, lo_off, j * ld + d, x);
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < n * half; idx += DC_THREADS) {
         const int j = idx / half, i = idx - j * half;
         const bf16* row = proj + (size_t)(tok0 + j) * a.ld;
         float sn, cs;
         sincosf((float)a.positions[tok0 + j] * a.freq[i], &sn, &cs);
-        if (qs != nullptr) {
+        if (WITH_Q) {
             float u = to_float(row[a.q_off + h * D + i]), v = to_float(row[a.q_off + h * D + i + half]);
             if (act) { u = da_silu(u); v = da_silu(v); }
             dc_put<SPLIT>(qs, lo_off, j * ld + i, u * cs - v * sn);
             dc_put<SPLIT>(qs, lo_off, j * ld + i + half, v * cs + u * sn);
         }
-        if (ks != nullptr) {
-            float u = to_float(row[a.k_off + h * D + i]), v = to_float(row[a.k_off + h * D + i + half]);
-            if (act) { u = da_silu(u); v = da_silu(v); }
-            dc_put<SPLIT>(ks, lo_off, j * ld + i, (u * cs - v * sn) * a.k_scale);
-            dc_put<SPLIT>(ks, lo_off, j * ld + i + half, (v * cs + u * sn) * a.k_scale);
-        }
+        float u = to_float(row[a.k_off + h * D + i]), v = to_float(row[a.k_off + h * D + i + half]);
+        if (act) { u = da_silu(u); v = da_silu(v); }
+        dc_put<SPLIT>(ks, lo_off, j * ld + i, (u * cs - v * sn) * a.k_scale);
+        dc_put<SPLIT>(ks, lo_off, j * ld + i + half, (v * cs + u * sn) * a.k_scale);
     }
     for (int idx = threadIdx.x; idx < n * rest; idx += DC_THREADS) {
         const int j = idx / rest, d = a.rot_dims + (idx - j * rest);
         const bf16* row = proj + (size_t)(tok0 + j) * a.ld;
-        if (qs != nullptr) {
+        if (WITH_Q) {
             float u = to_float(row[a.q_off + h * D + d]);
             if (act) u = da_silu(u);
             dc_put<SPLIT>(qs, lo_off, j * ld + d, u);
         }
-        if (ks != nullptr) {
-            float u = to_float(row[a.k_off + h * D + d]);
-            if (act) u = da_silu(u);
-            dc_put<SPLIT>(ks, lo_off, j * ld + d, u * a.k_scale);
-        }
+        float u = to_float(row[a.k_off + h * D + d]);
+        if (act) u = da_silu(u);
+        dc_put<SPLIT>(ks, lo_off, j * ld + d, u * a.k_scale);
     }
 }
 
@@ -116,12 +184,28 @@ template <bool SPLIT>
 __device__ __forceinline__ void dc_stage_v(bf16* vs, int lo_off, const bf16* proj, int tok0, int n, int h, int e0,
                                            const float* pw, const DecayAttnArgs& a) {
     const int width = min(DC_EV, a.Dv - e0);
+    const bool act = a.act == 1;
+    if (((a.ld | a.v_off | a.Dv) & 7) == 0 && (reinterpret_cast<size_t>(proj) & 15) == 0) {
+        const int wv = width >> 3;
+        for (int idx = threadIdx.x; idx < n * wv; idx += DC_THREADS) {
+            const int j = idx / wv, col = (idx - j * wv) << 3;
+            float x[8];
+            dc_load8(x, proj + (size_t)(tok0 + j) * a.ld + a.v_off + h * a.Dv + e0 + col, act);
+            if (pw != nullptr) {
+                const float w = pw[n - 1 - j];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] *= w;
+            }
+            dc_put8<SPLIT>(vs, lo_off, j * DC_LDV + col, x);
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < n * width; idx += DC_THREADS) {
-        const int j = idx / width, c = idx - j * width;
-        float v = to_float(proj[(size_t)(tok0 + j) * a.ld + a.v_off + h * a.Dv + e0 + c]);
-        if (a.act == 1) v = da_silu(v);
+        const int j = idx / width, col = idx - j * width;
+        float v = to_float(proj[(size_t)(tok0 + j) * a.ld + a.v_off + h * a.Dv + e0 + col]);
+        if (act) v = da_silu(v);
         if (pw != nullptr) v *= pw[n - 1 - j];
-        dc_put<SPLIT>(vs, lo_off, j * DC_LDV + c, v);
+        dc_put<SPLIT>(vs, lo_off, j * DC_LDV + col, v);
     }
 }
 
@@ -145,10 +229,11 @@ __global__ void __launch_bounds__(DC_THREADS) decay_chunk_local_kernel(const Dec
     bf16* vs = ks + parts * k_elems;                        // [parts][64][DC_LDV]
     float* pw = reinterpret_cast<float*>(vs + parts * v_elems);
     dc_powers(pw, a.decay[h]);
-    dc_zero(ks, parts * (k_elems + v_elems) * (int)sizeof(bf16));
+    if (n < DC_CHUNK || D < Dp || Dv - e0 < DC_EV)          // (a full tile is written whole)
+        dc_zero(ks, parts * (k_elems + v_elems) * (int)sizeof(bf16));
     __syncthreads();
     const bf16* proj = reinterpret_cast<const bf16*>(a.proj);
-    dc_stage_qk<SPLIT>(nullptr, ks, ldk, k_elems, proj, q0 + row0, n, h, a);
+    dc_stage_qk<SPLIT, false>(nullptr, ks, ldk, k_elems, proj, q0 + row0, n, h, a);
     dc_stage_v<SPLIT>(vs, v_elems, proj, q0 + row0, n, h, e0, pw, a);
     __syncthreads();
 
@@ -183,8 +268,12 @@ __global__ void __launch_bounds__(DC_THREADS) decay_chunk_local_kernel(const Dec
             for (int half = 0; half < 2; ++half) {
                 const int d = mt * 16 + g + half * 8;
                 if (d < D) {
-                    if (e < Dv) dst[(size_t)d * Dv + e] = acc[nt][2 * half];
-                    if (e + 1 < Dv) dst[(size_t)d * Dv + e + 1] = acc[nt][2 * half + 1];
+                    if (e + 1 < Dv && !(Dv & 1))
+                        *reinterpret_cast<float2*>(dst + (size_t)d * Dv + e) = make_float2(acc[nt][2 * half], acc[nt][2 * half + 1]);
+                    else {
+                        if (e < Dv) dst[(size_t)d * Dv + e] = acc[nt][2 * half];
+                        if (e + 1 < Dv) dst[(size_t)d * Dv + e + 1] = acc[nt][2 * half + 1];
+                    }
                 }
             }
         }
@@ -216,21 +305,29 @@ __global__ void __launch_bounds__(256) decay_chunk_scan_kernel(const DecayChunkA
     float* wp = c.work + ((size_t)first * a.H + h) * (size_t)elems + idx;
     const size_t step = (size_t)a.H * elems;
     float S = *sp;
-    float L = *wp;
-    for (int k = 0; k < count; ++k) {
-        const float L_next = k + 1 < count ? wp[step] : 0.f;
-        const int n = min(DC_CHUNK, qlen - k * DC_CHUNK);
-        *wp = S;
-        S = fmaf(n == DC_CHUNK ? g_full : powf(g, (float)n), S, L);
-        L = L_next;
-        wp += step;
+    // (the loads of a batch do not wait for one another: one memory latency a batch, not a chunk)
+    for (int k0 = 0; k0 < count; k0 += DC_SCAN_BATCH) {
+        float L[DC_SCAN_BATCH];
+#pragma unroll
+        for (int u = 0; u < DC_SCAN_BATCH; ++u) L[u] = k0 + u < count ? wp[u * step] : 0.f;
+#pragma unroll
+        for (int u = 0; u < DC_SCAN_BATCH; ++u) {
+            if (k0 + u < count) {
+                const int n = min(DC_CHUNK, qlen - (k0 + u) * DC_CHUNK);
+                wp[u * step] = S;
+                S = fmaf(n == DC_CHUNK ? g_full : powf(g, (float)n), S, L[u]);
+            }
+        }
+        wp += DC_SCAN_BATCH * step;
     }
     *sp = S;
 }
 
 // ------------------------------------------------------------------ 3. the chunk's outputs
-// Four warps, 16 tokens each.  The masked scores stay in registers: the accumulator of q . k^T of
-// 16 tokens x 16 keys has the layout of the A operand of the product with v.
+// Eight warps: 16 tokens and 32 of the value columns each (the scores of 16 tokens are formed by the
+// two warps that share them).  The masked scores stay in registers: the accumulator of q . k^T of
+// 16 tokens x 16 keys has the layout of the A operand of the product with v.  The entering state's
+// tile takes the place of the keys once the scores are formed (two blocks fit an SM that way).
 template <bool SPLIT>
 __global__ void __launch_bounds__(DC_THREADS) decay_chunk_out_kernel(const DecayChunkArgs c) {
     extern __shared__ __align__(16) unsigned char dc_smem[];
@@ -247,85 +344,108 @@ __global__ void __launch_bounds__(DC_THREADS) decay_chunk_out_kernel(const Decay
     const int D = a.D, Dv = a.Dv, Dp = (D + 15) & ~15;
     const int ldk = Dp + DC_PAD;
     const int qk_elems = DC_CHUNK * ldk, v_elems = DC_CHUNK * DC_LDV, s_elems = Dp * DC_LDV;
+    const int ks_elems = max(qk_elems, s_elems);            // a part of the queries, and of the keys, then the state's tile
     const int parts = SPLIT ? 2 : 1;
-    bf16* qs = reinterpret_cast<bf16*>(dc_smem);            // [parts][64][ldk]
-    bf16* ks = qs + parts * qk_elems;                       // [parts][64][ldk]
-    bf16* vs = ks + parts * qk_elems;                       // [parts][64][DC_LDV]
-    bf16* ss = vs + parts * v_elems;                        // [parts][Dp][DC_LDV]
-    float* pw = reinterpret_cast<float*>(ss + parts * s_elems);
+    bf16* qs = reinterpret_cast<bf16*>(dc_smem);            // [parts][64][ldk] (parts ks_elems apart)
+    bf16* ks = qs + parts * ks_elems;                       // [parts][64][ldk], later [parts][Dp][DC_LDV]
+    bf16* vs = ks + parts * ks_elems;                       // [parts][64][DC_LDV]
+    float* pw = reinterpret_cast<float*>(vs + parts * v_elems);
+    const int width = min(DC_EV, Dv - e0);
     dc_powers(pw, a.decay[h]);
-    dc_zero(qs, parts * (2 * qk_elems + v_elems + s_elems) * (int)sizeof(bf16));
+    if (n < DC_CHUNK || D < Dp || width < DC_EV)            // (a full tile is written whole)
+        dc_zero(qs, parts * (2 * ks_elems + v_elems) * (int)sizeof(bf16));
     __syncthreads();
     const bf16* proj = reinterpret_cast<const bf16*>(a.proj);
     const int tok0 = q0 + row0;
-    dc_stage_qk<SPLIT>(qs, ks, ldk, qk_elems, proj, tok0, n, h, a);
+    dc_stage_qk<SPLIT, true>(qs, ks, ldk, ks_elems, proj, tok0, n, h, a);
     dc_stage_v<SPLIT>(vs, v_elems, proj, tok0, n, h, e0, nullptr, a);
-    {
-        const float* src = c.work + ((size_t)tile * a.H + h) * (size_t)D * Dv;
-        const int width = min(DC_EV, Dv - e0);
-        for (int idx = threadIdx.x; idx < D * width; idx += DC_THREADS) {
-            const int d = idx / width, col = idx - d * width;
-            dc_put<SPLIT>(ss, s_elems, d * DC_LDV + col, src[(size_t)d * Dv + e0 + col]);
-        }
-    }
     __syncthreads();
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    if (warp * 16 >= n) return;                             // (no barrier follows)
+    const int warp = (threadIdx.x >> 5) & 3, wc = threadIdx.x >> 7;     // token group, half of the columns
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const bool live = warp * 16 < n;
     const int a_row = (warp * 16 + (lane & 15)) * ldk + ((lane >> 4) & 1) * 8;   // A[m = token][k = d], + kk * 16
 
     // scores of this warp's tokens against the keys up to its own 16
     float p[8][4];
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) p[nt][0] = p[nt][1] = p[nt][2] = p[nt][3] = 0.f;
-    for (int kk = 0; kk < Dp / 16; ++kk) {
-        unsigned ah[4], al[4] = {0, 0, 0, 0};
-        ldmatrix_x4(ah, qs + a_row + kk * 16);
-        if (SPLIT) ldmatrix_x4(al, qs + qk_elems + a_row + kk * 16);
+    if (live) {
+        for (int kk = 0; kk < Dp / 16; ++kk) {
+            unsigned ah[4], al[4] = {0, 0, 0, 0};
+            ldmatrix_x4(ah, qs + a_row + kk * 16);
+            if (SPLIT) ldmatrix_x4(al, qs + ks_elems + a_row + kk * 16);
 #pragma unroll
-        for (int np = 0; np < 4; ++np) {
-            if (np <= warp) {
-                // B[k = d][n = key] from rows stored [key][d]
-                const int b_at = (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * ldk + kk * 16 + ((lane >> 3) & 1) * 8;
-                unsigned bh[4], bl[4] = {0, 0, 0, 0};
-                ldmatrix_x4(bh, ks + b_at);
-                if (SPLIT) ldmatrix_x4(bl, ks + qk_elems + b_at);
-                dc_mma<SPLIT>(p[2 * np], ah, al, bh[0], bh[1], bl[0], bl[1]);
-                dc_mma<SPLIT>(p[2 * np + 1], ah, al, bh[2], bh[3], bl[2], bl[3]);
+            for (int np = 0; np < 4; ++np) {
+                if (np <= warp) {
+                    // B[k = d][n = key] from rows stored [key][d]
+                    const int b_at = (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * ldk + kk * 16 + ((lane >> 3) & 1) * 8;
+                    unsigned bh[4], bl[4] = {0, 0, 0, 0};
+                    ldmatrix_x4(bh, ks + b_at);
+                    if (SPLIT) ldmatrix_x4(bl, ks + ks_elems + b_at);
+                    dc_mma<SPLIT>(p[2 * np], ah, al, bh[0], bh[1], bl[0], bl[1]);
+                    dc_mma<SPLIT>(p[2 * np + 1], ah, al, bh[2], bh[3], bl[2], bl[3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int i = warp * 16 + g + 8 * (r >> 1), j = nt * 8 + 2 * t + (r & 1);
+                p[nt][r] = (j <= i && i < n) ? p[nt][r] * pw[i - j] : 0.f;
+            }
+    }
+    __syncthreads();                                        // every warp is done with the keys
+
+    // the entering state's tile [d][e] over them (padding rows and columns zero)
+    {
+        const float* src = c.work + ((size_t)tile * a.H + h) * (size_t)D * Dv + e0;
+        if (D < Dp || width < DC_EV) dc_zero(ks, parts * ks_elems * (int)sizeof(bf16));
+        if (D < Dp || width < DC_EV) __syncthreads();
+        if ((Dv & 7) == 0) {
+            const int wv = width >> 3;
+#pragma unroll 4
+            for (int idx = threadIdx.x; idx < D * wv; idx += DC_THREADS) {
+                const int d = idx / wv, col = (idx - d * wv) << 3;
+                const float4 lo4 = *reinterpret_cast<const float4*>(src + (size_t)d * Dv + col);
+                const float4 hi4 = *reinterpret_cast<const float4*>(src + (size_t)d * Dv + col + 4);
+                const float x[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
+                dc_put8<SPLIT>(ks, ks_elems, d * DC_LDV + col, x);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < D * width; idx += DC_THREADS) {
+                const int d = idx / width, col = idx - d * width;
+                dc_put<SPLIT>(ks, ks_elems, d * DC_LDV + col, src[(size_t)d * Dv + col]);
             }
         }
     }
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int i = warp * 16 + g + 8 * (r >> 1), j = nt * 8 + 2 * t + (r & 1);
-            p[nt][r] = (j <= i && i < n) ? p[nt][r] * pw[i - j] : 0.f;
-        }
+    __syncthreads();
+    if (!live) return;                                      // (no barrier follows)
 
     // what the entering state gives: q . S, each token's row times g^(i + 1)
-    float acc[8][4];
+    float acc[4][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    for (int nt = 0; nt < 4; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
     for (int kk = 0; kk < Dp / 16; ++kk) {
         unsigned ah[4], al[4] = {0, 0, 0, 0};
         ldmatrix_x4(ah, qs + a_row + kk * 16);
-        if (SPLIT) ldmatrix_x4(al, qs + qk_elems + a_row + kk * 16);
+        if (SPLIT) ldmatrix_x4(al, qs + ks_elems + a_row + kk * 16);
 #pragma unroll
-        for (int np = 0; np < 4; ++np) {
+        for (int np = 0; np < 2; ++np) {
             // B[k = d][n = e] from rows stored [d][e]
-            const int b_at = (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DC_LDV + np * 16 + ((lane >> 4) & 1) * 8;
+            const int b_at = (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DC_LDV + (wc * 2 + np) * 16 + ((lane >> 4) & 1) * 8;
             unsigned bh[4], bl[4] = {0, 0, 0, 0};
-            ldmatrix_x4_trans(bh, ss + b_at);
-            if (SPLIT) ldmatrix_x4_trans(bl, ss + s_elems + b_at);
+            ldmatrix_x4_trans(bh, ks + b_at);
+            if (SPLIT) ldmatrix_x4_trans(bl, ks + ks_elems + b_at);
             dc_mma<SPLIT>(acc[2 * np], ah, al, bh[0], bh[1], bl[0], bl[1]);
             dc_mma<SPLIT>(acc[2 * np + 1], ah, al, bh[2], bh[3], bl[2], bl[3]);
         }
     }
     {
-        const float f0 = pw[min(warp * 16 + g + 1, DC_CHUNK)], f1 = pw[min(warp * 16 + g + 9, DC_CHUNK)];
+        const float f0 = pw[warp * 16 + g + 1], f1 = pw[warp * 16 + g + 9];
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < 4; ++nt) {
             acc[nt][0] *= f0; acc[nt][1] *= f0;
             acc[nt][2] *= f1; acc[nt][3] *= f1;
         }
@@ -346,9 +466,9 @@ __global__ void __launch_bounds__(DC_THREADS) decay_chunk_out_kernel(const Decay
                 }
             }
 #pragma unroll
-            for (int np = 0; np < 4; ++np) {
+            for (int np = 0; np < 2; ++np) {
                 // B[k = key][n = e] from rows stored [key][e]
-                const int b_at = (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DC_LDV + np * 16 + ((lane >> 4) & 1) * 8;
+                const int b_at = (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DC_LDV + (wc * 2 + np) * 16 + ((lane >> 4) & 1) * 8;
                 unsigned bh[4], bl[4] = {0, 0, 0, 0};
                 ldmatrix_x4_trans(bh, vs + b_at);
                 if (SPLIT) ldmatrix_x4_trans(bl, vs + v_elems + b_at);
@@ -357,16 +477,20 @@ __global__ void __launch_bounds__(DC_THREADS) decay_chunk_out_kernel(const Decay
             }
         }
     }
+    const bool pairs = !((Dv | a.ldo) & 1);
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-        const int e = e0 + nt * 8 + 2 * t;
+    for (int nt = 0; nt < 4; ++nt) {
+        const int e = e0 + (wc * 4 + nt) * 8 + 2 * t;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int i = warp * 16 + g + half * 8;
             if (i < n) {
                 float* o = a.out + (size_t)(tok0 + i) * a.ldo + h * Dv;
-                if (e < Dv) o[e] = acc[nt][2 * half];
-                if (e + 1 < Dv) o[e + 1] = acc[nt][2 * half + 1];
+                if (pairs && e + 1 < Dv) *reinterpret_cast<float2*>(o + e) = make_float2(acc[nt][2 * half], acc[nt][2 * half + 1]);
+                else {
+                    if (e < Dv) o[e] = acc[nt][2 * half];
+                    if (e + 1 < Dv) o[e + 1] = acc[nt][2 * half + 1];
+                }
             }
         }
     }
@@ -378,8 +502,8 @@ static size_t dc_local_smem(int D, bool split) {
 }
 static size_t dc_out_smem(int D, bool split) {
     const int Dp = (D + 15) & ~15, parts = split ? 2 : 1;
-    return (size_t)parts * (2 * DC_CHUNK * (Dp + DC_PAD) + DC_CHUNK * DC_LDV + Dp * DC_LDV) * sizeof(bf16) +
-           (DC_CHUNK + 4) * sizeof(float);
+    const int qk = DC_CHUNK * (Dp + DC_PAD), st = Dp * DC_LDV;
+    return (size_t)parts * (2 * (qk > st ? qk : st) + DC_CHUNK * DC_LDV) * sizeof(bf16) + (DC_CHUNK + 4) * sizeof(float);
 }
 
 template <bool SPLIT>

@@ -154,6 +154,7 @@ def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk,
 
 
 # ------------------------------------------------- several attention maps a head
+use_maps_tc = True         # steps with prompt portions: the tcgen05 kernel where it takes the sizes
 def prepare_maps_attention(key_dim: int, value_dim: int, dtype: torch.dtype) -> None:
     """Builds what ``maps_attention`` will launch for these sizes (at load, not in a step)."""
     if _kv_fast(key_dim, value_dim, dtype) and torch.cuda.is_available():
@@ -164,8 +165,15 @@ def maps_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, maps, Dk, Dv, p
     """Attention with ``maps`` maps a head (q [T, H, maps, Dk]; a cached key row holds a kv head's
     maps side by side; one set of values a kv head), causal with an optional window; float32
     results per map, [T, H, maps, Dv].  bfloat16 with sizes in multiples of 16: the tensor-core
-    kernel built for the pair of sizes; float32 or other sizes: the plain kernel."""
+    kernels built for the pair of sizes (tcgen05 for prompt portions with sizes in multiples of
+    64, mma.sync otherwise); float32 or other sizes: the plain kernel."""
     if _kv_fast(Dk, Dv, q.dtype) and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0:
+        if (use_maps_tc and not ctx.decode_only and out.stride(0) % 4 == 0
+                and K.attention_kv_tc_takes(Dk, Dv, page_size, H // Hkv, False)):
+            # steps with portions of prompts, sizes in multiples of 64: the tcgen05 kernel
+            K.attention_kv_tc_maps(ctx, q, k_cache, v_cache, out, table, H, Hkv, maps, Dk, Dv, page_size, scale,
+                                   window)
+            return
         K.attention_kv_mma_maps(ctx, q, k_cache, v_cache, out, table, H, Hkv, maps, Dk, Dv, page_size, scale, window)
         return
     K.attention_kv_maps(ctx, q, k_cache, v_cache, out, table, H, Hkv, maps, Dk, Dv, page_size, scale, window)

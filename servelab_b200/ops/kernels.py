@@ -983,6 +983,20 @@ def attention_kv_tc(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num_
         head_gate.stride(0) if head_gate is not None else 0, _stream()), "attention_kv_tc")
 
 
+def attention_kv_tc_maps(ctx, q, k_cache, v_cache, out, block_table, num_heads: int, num_kv_heads: int,
+                         maps: int, k_dim: int, v_dim: int, page_size: int, scale: float, window: int = 0) -> None:
+    """The tcgen05 kernel with ``maps`` attention maps a head (layouts as ``attention_kv_maps``): a
+    block takes 128 flattened rows of one map of a kv head; float32 results per map."""
+    lib = L.attention_kv(k_dim, v_dim)
+    group = num_heads // num_kv_heads
+    tile_seq, tile_row0, n = ctx.attention_tiles(group, lib.slb_attention_kv_tc_tile_rows(group))
+    L.check(lib.slb_attention_kv_tc_maps_bf16(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), out.stride(0),
+        block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_len.data_ptr(),
+        tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads, maps, page_size,
+        k_cache.shape[0], float(scale), int(window), _stream()), "attention_kv_tc")
+
+
 def attention_kv_tc_status(k_dim: int, v_dim: int, reset: bool = False) -> int:
     """0, or the code of the first bounded wait of the tcgen05 kernel that gave up."""
     return L.attention_kv(k_dim, v_dim).slb_attention_kv_tc_status(1 if reset else 0)
