@@ -9,8 +9,8 @@ heads mixed after the softmax -- which this package computes as one attention re
 (query head, kv head) pair, so its attention does kv_heads times the arithmetic of the plain
 one.  ``python bench.py --compare dezelorn`` prints one JSON line with, per size and model:
 prefill tokens per second (one 2,048-token prompt), decode tokens per second at batch 8 and 64
-(contexts of 1,536 tokens, graphs), and per-kernel microseconds of an eager prefill and an
-eager decode step of 8 requests.
+(contexts of 1,536 tokens, graphs), and per-kernel microseconds of an eager prefill and of
+eager decode steps of 8 and of 64 requests.
 """
 
 from __future__ import annotations
@@ -203,9 +203,9 @@ def daferax_like_zimupel(width, heads, kv, dim, experts, groups, keep, top, eff,
 def _zimupel_rooflines(size, res, peaks) -> Dict[str, object]:
     """Microseconds per launch and achieved fractions of the measured peaks for the kernels of the
     Zimupel layers beside their Daferax counterparts, from the eager profiles.  Linear attention,
-    prefill: 4 T H D Dv flops (state update and output, the recurrence's own arithmetic, float32 on
-    CUDA cores) of the bf16 peak, beside the softmax attention's 2 (Dk + Dv) flops per visible pair
-    and head; decode: the state read and written once, of the copy bandwidth, beside the cached
+    prefill: 4 T H D Dv flops (state update and output, the recurrence's own arithmetic; the chunked
+    kernels spend more, on the tensor cores) of the bf16 peak, beside the softmax attention's
+    2 (Dk + Dv) flops per visible pair and head; decode: the state read and written once, of the copy bandwidth, beside the cached
     rows the requests may see.  Elementwise kernels: the bytes they must move, of the copy
     bandwidth."""
     width, heads, kv, dim, experts, groups, keep, top, eff, streams = ZIMUPEL_SIZES[size]
@@ -221,15 +221,16 @@ def _zimupel_rooflines(size, res, peaks) -> Dict[str, object]:
     def tf(flops, us):
         return round(flops / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
 
-    if zp.get("decay_attention"):
-        us = zp["decay_attention"] / n_lin
+    lin = (zp.get("decay_attention (chunked)") or 0) + (zp.get("decay_attention") or 0)
+    if lin:
+        us = lin / n_lin
         out["zimupel_linear_prefill_us_per_layer"] = round(us, 1)
         out["zimupel_linear_prefill_bf16_frac"] = tf(4.0 * PROMPT * heads * dim * dim, us)
     if zd.get("decay_attention"):
         us = zd["decay_attention"] / n_lin
         out["zimupel_linear_decode_us_per_layer"] = round(us, 2)
         out["zimupel_linear_decode_hbm_frac"] = hbm(8 * 2 * heads * dim * dim * 4, us)
-    zatt = zp.get("attention_kv_mma") or zp.get("attention_kv_maps")
+    zatt = zp.get("attention_kv_tc") or zp.get("attention_kv_mma") or zp.get("attention_kv_maps")
     if zatt:
         us = zatt / n_att
         out["zimupel_differential_prefill_us_per_layer"] = round(us, 1)
@@ -331,14 +332,13 @@ def _measure(cfg: dict, note) -> Dict[str, object]:
         ms = timed(lambda: K.sample_rows(runner.step(entries), tok), 50, 10)
         out[f"decode_b{batch}_ms"] = round(ms, 4)
         out[f"decode_b{batch}_tok_s"] = round(batch / (ms * 1e-3), 1)
-        if batch == 8:
-            runner.cuda_graphs = False
-            runner.step(entries)
-            with StepProfile() as prof:
-                for _ in range(5):
-                    runner.step(entries)
-            out["decode_b8_kernels_us"] = prof.summary(5)
-            runner.cuda_graphs = saved
+        runner.cuda_graphs = False
+        runner.step(entries)
+        with StepProfile() as prof:
+            for _ in range(5):
+                runner.step(entries)
+        out[f"decode_b{batch}_kernels_us"] = prof.summary(5)
+        runner.cuda_graphs = saved
         for rid in rids:
             runner.cache.release(rid)
     del engine, runner

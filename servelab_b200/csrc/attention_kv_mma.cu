@@ -17,7 +17,11 @@
 // kernel combines them (and applies the gate).
 //
 // In a step of single tokens a tile holds the g query heads of one request that share the kv
-// head (all heads of a latent attention): the rows of the MMA are heads.
+// head (all heads of a latent attention): the rows of the MMA are heads.  When they are at most
+// 16 (`narrow`), the four warps share them: each forms the tile's scores and softmax weights (the
+// same numbers in every warp) and multiplies them with its quarter of the value columns, so the
+// long product of a tile is spread over the warps; the Q tile takes 16 rows of shared memory, so
+// that two blocks fit an SM at the largest sizes.
 //
 // Several attention maps a head (`maps`; not with `tied`): every query head and every kv head
 // carries `maps` query / key vectors side by side ([head][map][DK]; a cached key row is
@@ -77,11 +81,12 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
     const int* __restrict__ tile_row0, int H, int Hkv, int ps, int num_pages, float scale_log2,
     int window, const bf16* __restrict__ gate, int ldg, int splits, float* __restrict__ part_o,
-    float* __restrict__ part_ml, int maps, float* __restrict__ out_f32) {
+    float* __restrict__ part_ml, int maps, float* __restrict__ out_f32, int narrow) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
-    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDK]
-    bf16* stage0 = Qs + BM * LDK;                          // 2 x (K tile | V tile)
+    const int q_rows = narrow ? 16 : BM;
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [q_rows][LDK]
+    bf16* stage0 = Qs + q_rows * LDK;                      // 2 x (K tile | V tile)
     const int STAGE_ELEMS = stage_elems(tied != 0);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -95,12 +100,12 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     const int q0 = cu_q[s];
     const int qlen = cu_q[s + 1] - q0;
     const int ctx = ctx_len[s];
-    const int nrows = min(BM, qlen * g - row0);
+    const int nrows = min(q_rows, qlen * g - row0);
     if (nrows <= 0) return;
     const int pos_base = ctx - qlen;
     const int* table = block_table + (size_t)s * max_pages;
 
-    for (int idx = tid; idx < BM * KCH; idx += NTHREADS) {
+    for (int idx = tid; idx < q_rows * KCH; idx += NTHREADS) {
         const int r = idx / KCH, c = idx - r * KCH;
         const bool ok = r < nrows;
         const int rho = row0 + (ok ? r : 0);
@@ -126,12 +131,13 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         load_tile(stage0, stage0 + BN * LDK, kc, vc, tied != 0, table, kbeg, kend, kvh, Hkv, ps, num_pages, ldk, koff);
     cp_async_commit();
 
-    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+    const int wrow = narrow ? 0 : warp;                    // the warp's 16 rows of the tile
+    const int r_lo = wrow * 16 + (lane >> 2), r_hi = r_lo + 8;
     const int pos_lo = r_lo < nrows ? pos_base + (row0 + r_lo) / g : -1;
     const int pos_hi = r_hi < nrows ? pos_base + (row0 + r_hi) / g : -1;
-    const int wr_last = min(nrows - 1, warp * 16 + 15);
-    const int warp_pos_max = warp * 16 < nrows ? pos_base + (row0 + wr_last) / g : -1;
-    const int warp_pos_min = pos_base + (row0 + warp * 16) / g;
+    const int wr_last = min(nrows - 1, wrow * 16 + 15);
+    const int warp_pos_max = wrow * 16 < nrows ? pos_base + (row0 + wr_last) / g : -1;
+    const int warp_pos_min = pos_base + (row0 + wrow * 16) / g;
     const int tig = lane & 3;
 
     float o[NT_O][4];
@@ -140,7 +146,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    const bf16* Qw = Qs + warp * 16 * LDK;
+    const bf16* Qw = Qs + wrow * 16 * LDK;
 
     for (int t = 0; t < ntiles; ++t) {
         bf16* Ks = stage0 + (t & 1) * STAGE_ELEMS;
@@ -235,6 +241,18 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
                 a[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
                 a[3] = pack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
                 unsigned vf[2][4];
+                if (narrow) {                              // this warp's share of the value columns
+#pragma unroll
+                    for (int np = 0; np < NT_O / 2; ++np) {
+                        if ((np & 3) == warp) {
+                            ldmatrix_x4_trans(vf[0], Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s +
+                                                         np * 16 + (lane >> 4) * 8);
+                            mma_bf16(o[2 * np], a, vf[0][0], vf[0][1]);
+                            mma_bf16(o[2 * np + 1], a, vf[0][2], vf[0][3]);
+                        }
+                    }
+                    continue;
+                }
                 ldmatrix_x4_trans(vf[0], Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s + (lane >> 4) * 8);
 #pragma unroll
                 for (int np = 0; np < NT_O / 2; ++np) {
@@ -266,14 +284,15 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         const int head = (kvh * g + hg) * maps + map;
         if (splits > 1) {
             const size_t pi = ((size_t)(q0 + tl) * H * maps + head) * splits + blockIdx.y;
-            if (tig == 0) {
+            if (tig == 0 && (!narrow || warp == 0)) {
                 part_ml[2 * pi] = m[h];
                 part_ml[2 * pi + 1] = l[h];
             }
             float* po = part_o + pi * DV + tig * 2;
 #pragma unroll
             for (int n = 0; n < NT_O; ++n)
-                *reinterpret_cast<float2*>(po + n * 8) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+                if (!narrow || ((n >> 1) & 3) == warp)
+                    *reinterpret_cast<float2*>(po + n * 8) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
             continue;
         }
         float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
@@ -285,13 +304,15 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
             float* dst = out_f32 + (size_t)(q0 + tl) * ldo + (size_t)head * DV + tig * 2;
 #pragma unroll
             for (int n = 0; n < NT_O; ++n)
-                *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+                if (!narrow || ((n >> 1) & 3) == warp)
+                    *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
             continue;
         }
         bf16* dst = out + (size_t)(q0 + tl) * ldo + (size_t)head * DV + tig * 2;
 #pragma unroll
         for (int n = 0; n < NT_O; ++n)
-            *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+            if (!narrow || ((n >> 1) & 3) == warp)
+                *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
     }
 }
 
@@ -357,17 +378,20 @@ static int launch_attention_kv_mma(const bf16* q, int ldq, const bf16* kc, const
                                    const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
                                    int H, int Hkv, int maps, int ps, int num_pages, float scale, int window,
                                    const bf16* gate, int ldg, int splits, float* part_o, float* part_ml,
-                                   cudaStream_t st) {
+                                   int narrow, cudaStream_t st) {
+    // `narrow`: every tile of the list holds at most 16 rows (a step of single tokens with at most
+    // 16 query heads a kv head).
     // `splits` > 1 (steps of single tokens only: a tile is one token's heads): scratch part_o
     // [tokens][H * maps][splits][DV] and part_ml [tokens][H * maps][splits][2], float32.
     if (num_tiles <= 0) return 0;
     if (splits < 1 || splits > 32 || (splits > 1 && (part_o == nullptr || part_ml == nullptr || H / Hkv > BM)))
         return SLB_ERR_BAD_ARG;
+    if (narrow && H / Hkv > 16) return SLB_ERR_BAD_ARG;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || scale <= 0.f ||
         (tied && DV > DK) || ldq % 8 != 0 || ldo % 2 != 0 || maps < 1 || (maps > 1 && tied))
         return SLB_ERR_BAD_ARG;
     if ((long long)num_tiles * Hkv * maps > 2147483647LL) return SLB_ERR_TOO_LARGE;
-    const size_t smem = ((size_t)BM * LDK + 2 * stage_elems(tied != 0)) * sizeof(bf16);
+    const size_t smem = ((size_t)(narrow ? 16 : BM) * LDK + 2 * stage_elems(tied != 0)) * sizeof(bf16);
     static unsigned long long configured = 0;
     const int rc = slb_configure(&configured, attention_kv_mma_kernel,
                                  ((size_t)BM * LDK + 2 * stage_elems(false)) * sizeof(bf16));
@@ -375,7 +399,7 @@ static int launch_attention_kv_mma(const bf16* q, int ldq, const bf16* kc, const
     const int e = slb_launch(attention_kv_mma_kernel, dim3(num_tiles * Hkv * maps, splits), dim3(NTHREADS), smem, st,
                              q, ldq, kc, tied ? kc : vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len,
                              tile_seq, tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window,
-                             gate, ldg, splits, part_o, part_ml, maps, out_f32);
+                             gate, ldg, splits, part_o, part_ml, maps, out_f32, narrow ? 1 : 0);
     if (e != 0 || splits == 1) return e;
     // (one tile a token: num_tiles is the number of tokens)
     return slb_launch(attention_kv_combine_kernel, dim3(num_tiles, H * maps), dim3(128), 0, st, (const float*)part_o,
@@ -387,19 +411,19 @@ int slb_attention_kv_mma_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
                               const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
                               int H, int Hkv, int ps, int num_pages, float scale, int window,
                               const bf16* gate, int ldg, int splits, float* part_o, float* part_ml,
-                              cudaStream_t st) {
+                              int narrow, cudaStream_t st) {
     return launch_attention_kv_mma(q, ldq, kc, vc, tied, out, nullptr, ldo, block_table, max_pages, cu_q, ctx_len,
                                    tile_seq, tile_row0, num_tiles, H, Hkv, 1, ps, num_pages, scale, window, gate,
-                                   ldg, splits, part_o, part_ml, st);
+                                   ldg, splits, part_o, part_ml, narrow, st);
 }
 // `maps` attention maps a head; float32 results [token][head][map][DV] with rows `ldo` floats apart
 int slb_attention_kv_mma_maps_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int maps, float* out,
                                    int ldo, const int* block_table, int max_pages, const int* cu_q,
                                    const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
                                    int H, int Hkv, int ps, int num_pages, float scale, int window, int splits,
-                                   float* part_o, float* part_ml, cudaStream_t st) {
+                                   float* part_o, float* part_ml, int narrow, cudaStream_t st) {
     return launch_attention_kv_mma(q, ldq, kc, vc, 0, nullptr, out, ldo, block_table, max_pages, cu_q, ctx_len,
                                    tile_seq, tile_row0, num_tiles, H, Hkv, maps, ps, num_pages, scale, window,
-                                   nullptr, 0, splits, part_o, part_ml, st);
+                                   nullptr, 0, splits, part_o, part_ml, narrow, st);
 }
 }

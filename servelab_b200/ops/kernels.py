@@ -952,11 +952,15 @@ def attention_kv_mma(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num
         out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
         ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads,
         page_size, k_cache.shape[0], float(scale), int(window), _p(head_gate),
-        head_gate.stride(0) if head_gate is not None else 0, splits, _p(part_o), _p(part_ml), _stream()),
+        head_gate.stride(0) if head_gate is not None else 0, splits, _p(part_o), _p(part_ml),
+        1 if ctx.decode_only and attention_kv_narrow and num_heads // num_kv_heads <= 16 else 0, _stream()),
         "attention_kv_mma")
 
 
 attention_kv_split = True      # (off: one block a request and kv head, the twin)
+# steps of single tokens with at most 16 query heads a kv head: the block's warps share the rows
+# and split the value columns (off: a warp 16 rows, the twin)
+attention_kv_narrow = True
 
 
 attention_kv_use_tc = True     # steps with prompt portions: the tcgen05 kernel where it takes the sizes
@@ -1293,4 +1297,6 @@ def attention_kv_mma_maps(ctx, q, k_cache, v_cache, out, block_table, num_heads:
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), maps, out.data_ptr(), out.stride(0),
         block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_len.data_ptr(),
         tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads, page_size, k_cache.shape[0],
-        float(scale), int(window), splits, _p(part_o), _p(part_ml), _stream()), "attention_kv_mma")
+        float(scale), int(window), splits, _p(part_o), _p(part_ml),
+        1 if ctx.decode_only and attention_kv_narrow and num_heads // num_kv_heads <= 16 else 0, _stream()),
+        "attention_kv_mma")

@@ -423,12 +423,17 @@ def test_attention_with_two_maps(dtype, shape, spike, monkeypatch):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(4, 1, 64, 128, 16), (4, 2, 48, 96, 32), (3, 3, 10, 6, 4)])
-def test_attention_with_two_maps_single_tokens_at_long_contexts(dtype, shape):
+@pytest.mark.parametrize("shape", [(4, 1, 64, 128, 16), (4, 2, 48, 96, 32), (3, 3, 10, 6, 4), (8, 2, 128, 256, 16),
+                                   (40, 2, 32, 48, 8)])
+@pytest.mark.parametrize("narrow", [True, False])
+def test_attention_with_two_maps_single_tokens_at_long_contexts(dtype, shape, narrow, monkeypatch):
     """A step of single tokens only (few requests, long contexts: the tensor-core kernel splits the
-    keys over blocks), with a dominant key 900 tokens back in the second map."""
+    keys over blocks), with a dominant key 900 tokens back in the second map.  ``narrow``: the
+    warps of a block share the (at most 16) rows and split the value columns; off, and with more
+    than 16 heads a kv head: a warp 16 rows."""
     from servelab_b200.ops import attention as A
     from servelab_b200.ops import kernels as K
+    monkeypatch.setattr(K, "attention_kv_narrow", narrow)
     Hq, G, D, Dv, ps = shape
     ctxs, qlens = [1400, 901, 1000], [1, 1, 1]
     q, kc, vc, want, entries = _maps_case(5 + D, Hq, G, D, Dv, ctxs, qlens, ps, dtype, 900)
