@@ -57,21 +57,26 @@ __device__ __forceinline__ void load_tile(bf16* Ks, bf16* Vs, const bf16* __rest
                                           const bf16* __restrict__ vc, bool tied,
                                           const int* __restrict__ table, int k0, int kend, int kvh,
                                           int Hkv, int ps, int num_pages, int ldk, int koff) {
+    // NTHREADS / BN threads a key: its page is looked up once, then its 16-byte chunks are shared out
+    constexpr int TPR = NTHREADS / BN;
+    static_assert(NTHREADS % BN == 0, "whole threads per key row");
     const int per_row = tied ? KCH : KCH + VCH;
-    for (int idx = threadIdx.x; idx < BN * per_row; idx += NTHREADS) {
-        const int r = idx / per_row, c = idx - r * per_row;
-        const int kp = k0 + r;
-        bool ok = kp < kend;
-        int page = -1;
-        if (ok) page = table[kp / ps];
-        if (page >= num_pages) {
-            atomicCAS(&kv_attn_status_word, 0, 0x40);
-            page = -1;
-        }
-        ok = ok && page >= 0;
-        const size_t slot = ok ? ((size_t)page * Hkv + kvh) * ps + kp % ps : 0;
-        if (c < KCH) cp_async16(Ks + r * LDK + c * 8, kc + slot * ldk + koff + c * 8, ok);
-        else cp_async16(Vs + r * LDV + (c - KCH) * 8, vc + slot * DV + (c - KCH) * 8, ok);
+    const int r = threadIdx.x / TPR, sub = threadIdx.x % TPR;
+    const int kp = k0 + r;
+    bool ok = kp < kend;
+    int page = -1;
+    if (ok) page = table[kp / ps];
+    if (page >= num_pages) {
+        atomicCAS(&kv_attn_status_word, 0, 0x40);
+        page = -1;
+    }
+    ok = ok && page >= 0;
+    const size_t slot = ok ? ((size_t)page * Hkv + kvh) * ps + kp % ps : 0;
+    const bf16* krow = kc + slot * ldk + koff;
+    const bf16* vrow = vc + slot * DV;
+    for (int c = sub; c < per_row; c += TPR) {
+        if (c < KCH) cp_async16(Ks + r * LDK + c * 8, krow + c * 8, ok);
+        else cp_async16(Vs + r * LDV + (c - KCH) * 8, vrow + (c - KCH) * 8, ok);
     }
 }
 
