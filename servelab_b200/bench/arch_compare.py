@@ -181,13 +181,13 @@ def zimupel_config(width, heads, kv, dim, experts, groups, keep, top, eff, strea
     mlp = {"kind": "moe", "expert": {"ff": eff},
            "router": {"experts": experts, "groups": {"count": groups, "keep": keep}, "top": top}}
     decay = [1.0 - 2.0 ** (-5 - 0.5 * i) for i in range(heads)]
-    ret = {"heads": heads, "dim": dim, "vdim": dim, "decay": decay, "rot": {"base": 1000000.0, "dims": dim}}
+    ret = {"heads": heads, "dim": dim, "vdim": dim, "decay": decay, "rot": {"base": 500000.0, "dims": dim}}
     lig = {"heads": heads, "dim": dim, "vdim": dim, "decay": decay}
     att = {"heads": heads // 2, "kv_heads": max(1, kv // 2), "dim": dim, "vdim": 2 * dim, "scale": dim ** -0.5,
-           "diff": 0.3}
+           "diff": 0.25}
     kinds = [("retention", ret), ("attention", att), ("lightning", lig), ("attention", dict(att, kv_from=1))]
     return {"architecture": "Zimupel", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5}, "streams": streams,
-            "logit_scale": 1.0, "logit_softcap": 30.0,
+            "logit_scale": 1.0, "logit_softcap": 25.0,
             "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(layers)]}
 
 

@@ -202,9 +202,6 @@ class ZimupelConfig:
             runs.append(LayerRun(i, cache_of=None if src is None else int(src)))
         if p:
             raise ConfigError("invalid Zimupel config: " + "; ".join(p))
-        if self.streams is None and any(b.feed_forward is None for b in layers):
-            raise ConfigError("invalid Zimupel config: a layer without feed-forward needs 'streams' "
-                              "(the single-stream block has no form without one)")
         return ModelSpec(
             architecture=self.architecture, hidden_size=self.width, vocab_size=self.vocab,
             layers=tuple(layers), run_order=tuple(runs), final_norm=norm, tie_word_embeddings=False,
@@ -212,6 +209,6 @@ class ZimupelConfig:
             lm_head_name="head", final_norm_prefix="final.norm", layer_prefix="l{}",
             embedding_norm=norm, embedding_norm_prefix="embed.norm", residual_streams=self.streams,
             logit_scale=self.logit_scale, logit_softcap=self.logit_softcap,
-            # a layer without a feed-forward has no use for its second norm and weights; a checkpoint
-            # may hold them all the same
-            ignored_suffixes=(".norm2",))
+            # a layer without a feed-forward has no use for its second norm and stream weights; a
+            # checkpoint may hold them all the same
+            ignored_suffixes=(".norm2", ".hc2.in", ".hc2.out", ".hc2.mix"))

@@ -1,7 +1,8 @@
 """Arrangement of a layer's parts.
 
 ``pre_norm``: x += mixer(norm1(x)); x += ff(norm2(x)) -- the order of the
-reference's layer body (servelab/parallel/tp_model.py:125-133).  The stream x is
+reference's layer body (servelab/parallel/tp_model.py:125-133); ``feed_forward``
+None: the layer ends after the mixer.  The stream x is
 float32; an update that has not been added yet travels beside it so that the add
 happens inside the next norm kernel.
 """
@@ -22,21 +23,26 @@ class PreNormBlock(Block):
         self._build(spec, prefix, env)
         # a step of this block may be captured in a CUDA graph iff every part only
         # launches kernels whose arguments are device buffers of the step context
-        self.graph_safe = all(getattr(p, "graph_safe", False) for p in
-                              (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward))
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in self._present())
 
     @staticmethod
     def _members(spec, prefix):
         """(registry, spec, prefix) of the four parts; the names under the layer's prefix are
         the spec's, so the block knows no checkpoint's naming."""
-        return ((NORMS, spec.mixer_norm, f"{prefix}.{spec.mixer_norm_name}"),
-                (MIXERS, spec.mixer, f"{prefix}.{spec.mixer_name}"),
-                (NORMS, spec.ff_norm, f"{prefix}.{spec.ff_norm_name}"),
-                (FEED_FORWARDS, spec.feed_forward, f"{prefix}.{spec.feed_forward_name}"))
+        out = ((NORMS, spec.mixer_norm, f"{prefix}.{spec.mixer_norm_name}"),
+               (MIXERS, spec.mixer, f"{prefix}.{spec.mixer_name}"))
+        if spec.feed_forward is None:                 # the layer ends after the mixer
+            return out
+        return out + ((NORMS, spec.ff_norm, f"{prefix}.{spec.ff_norm_name}"),
+                      (FEED_FORWARDS, spec.feed_forward, f"{prefix}.{spec.feed_forward_name}"))
 
     def _build(self, spec, prefix, env):
-        self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward = (
-            build_part(table, part, name, env) for table, part, name in self._members(spec, prefix))
+        parts = [build_part(table, part, name, env) for table, part, name in self._members(spec, prefix)]
+        self.mixer_norm, self.mixer = parts[:2]
+        self.ff_norm, self.feed_forward = parts[2:] if len(parts) > 2 else (None, None)
+
+    def _present(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None]
 
     @classmethod
     def declare(cls, spec, prefix):
@@ -50,7 +56,7 @@ class PreNormBlock(Block):
         return part_class(MIXERS, spec.mixer).cache_request(spec.mixer)
 
     def load(self, store):
-        for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward):
+        for p in self._present():
             p.load(store)
 
     accepts_split_sum = True          # the incoming ``delta`` may be a SplitSum
@@ -62,6 +68,8 @@ class PreNormBlock(Block):
         # that does not say that it takes the form gets the plain tensor.
         x = self.mixer_norm.forward(ctx, resid, plain_unless(self.mixer_norm, delta))
         a = self.mixer.forward(ctx, plain_unless(self.mixer, x), cache, owns_cache)
+        if self.feed_forward is None:
+            return resid, a
         x = self.ff_norm.forward(ctx, resid, plain_unless(self.ff_norm, a))
         return resid, self.feed_forward.forward(ctx, plain_unless(self.feed_forward, x))
 

@@ -63,7 +63,7 @@ def test_every_size_and_constant_reaches_the_spec():
     # without the keys: one residual, no scale, no cap, as many kv heads as heads
     q = config_from_dict(C.Q).to_model_spec()
     assert q.residual_streams is None and q.logit_scale is None and q.logit_softcap is None
-    assert [b.kind for b in q.layers] == ["pre_norm"] * 5 and q.layers[1].mixer.num_kv_heads == 3
+    assert [b.kind for b in q.layers] == ["pre_norm"] * 6 and q.layers[4].feed_forward is None and q.layers[1].mixer.num_kv_heads == 3
     assert config_from_dict(C.R).to_model_spec().residual_streams == 1
 
 

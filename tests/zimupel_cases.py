@@ -53,10 +53,11 @@ P = {"architecture": "Zimupel", "vocab": 211, "width": 48, "norm": {"eps": 1e-6}
                 layer(retention(1, 24, 40, (0.95,)), moe(5, 5, 8))]}
 # no streams: the single residual; no logit scale, no cap
 Q = {"architecture": "Zimupel", "vocab": 300, "width": 64, "norm": {"eps": 1e-5},
-     "layers": [layer(retention(4, 16, 16, (0.9, 0.99, 0.999, 0.8), rot=(1000000.0, 16)), dense(96)),
+     "layers": [layer(retention(4, 16, 16, (0.9, 0.99, 0.999, 0.8), rot=(200000.0, 16)), dense(96)),
                 layer(attention(3, None, 8, 24, 0.35, 0.5), moe(8, 3, 16, (4, 2))),
-                layer(lightning(1, 32, 16, (0.98,)), moe(8, 2, 32, (2, 1))),
+                layer(lightning(1, 32, 16, (0.98,)), moe(10, 2, 32, (2, 1))),
                 layer(attention(3, None, 8, 24, 0.2, 0.1, kv_from=1), dense(32)),
+                layer(lightning(2, 8, 8, (0.93, 0.75)), None),
                 layer(attention(2, 1, 32, 32, 0.18, 0.8), moe(4, 2, 16, (4, 2)))]}
 # one stream (with its weights), and sizes that no 16-byte access fits
 R = {"architecture": "Zimupel", "vocab": 97, "width": 50, "norm": {"eps": 1e-5}, "streams": 1,
@@ -70,7 +71,7 @@ S = {"architecture": "Zimupel", "vocab": 150, "width": 128, "norm": {"eps": 1e-5
      "layers": [layer(retention(2, 64, 64, (0.99, 0.9999), rot=(10000.0, 32)), moe(4, 2, 32, (2, 2))),
                 layer(attention(4, 1, 64, 128, 0.125, 0.6), dense(64)),
                 layer(lightning(2, 128, 64, (0.96, 0.999)), moe(8, 4, 16, (2, 1))),
-                layer(attention(4, 1, 64, 128, 0.1, 0.3, kv_from=1), moe(4, 1, 48))]}
+                layer(attention(4, 1, 64, 128, 0.1, 0.28, kv_from=1), moe(4, 1, 48))]}
 CASES = {"P": (P, 5, 8), "Q": (Q, 9, 16), "R": (R, 13, 4), "S": (S, 17, 16)}        # config, seed, page size
 # projections drawn large enough that the softmax of a tiny model is peaked and the router's
 # choice is clear of ties
