@@ -28,6 +28,12 @@
 // [map][DK]), each map is an attention of its own over the kv head's one set of values, and a
 // block owns (tile, kv head, map).  The results go out map by map, [token][head][map][DV], as
 // float32 when `out_f32` is given, for the kernel that combines the maps.
+//
+// Maps folded into the rows (`fold` maps, a library built for SLB_KEY_DIM = fold * the map's key
+// size): a (head, map) is a row of its own, and its query stands in the map's columns of an
+// otherwise zero row of SLB_KEY_DIM, so that the product with the whole cached key row
+// [map][key size] is that map's score.  One block then serves all maps of a kv head and reads
+// the values once; in a step of single tokens (memory-bound) that is the point.
 #include "mma_util.cuh"
 
 #ifndef SLB_KEY_DIM
@@ -80,16 +86,20 @@ __device__ __forceinline__ void load_tile(bf16* Ks, bf16* Vs, const bf16* __rest
     }
 }
 
+// NARROW: at most 16 rows a tile, shared by the warps; a warp then holds only its share of the
+// value columns (16-column pairs np with np % 4 == warp), and the Q tile takes `q_rows` = 8 or 16
+// rows of shared memory (with 8, the MMA's upper rows re-read the lower ones and are masked).
+template <bool NARROW>
 __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
     int tied, bf16* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
     const int* __restrict__ tile_row0, int H, int Hkv, int ps, int num_pages, float scale_log2,
     int window, const bf16* __restrict__ gate, int ldg, int splits, float* __restrict__ part_o,
-    float* __restrict__ part_ml, int maps, float* __restrict__ out_f32, int narrow) {
+    float* __restrict__ part_ml, int maps, float* __restrict__ out_f32, int q_rows, int fold) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
-    const int q_rows = narrow ? 16 : BM;
+    constexpr int NO = NARROW ? ((NT_O / 2 + 3) / 4) * 2 : NT_O;      // 8-column tiles of O a warp holds
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [q_rows][LDK]
     bf16* stage0 = Qs + q_rows * LDK;                      // 2 x (K tile | V tile)
     const int STAGE_ELEMS = stage_elems(tied != 0);
@@ -115,6 +125,13 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         const bool ok = r < nrows;
         const int rho = row0 + (ok ? r : 0);
         const int tl = rho / g, hg = rho - tl * g;
+        if (fold > 1) {
+            // H counts (head, map) pairs; the pair's query of DK / fold elements goes to its map's columns
+            const int dks = DK / fold, pair = kvh * g + hg, at = c * 8 - (pair % fold) * dks;
+            const bool mine = ok && at >= 0 && at < dks;
+            cp_async16(Qs + r * LDK + c * 8, q + (size_t)(q0 + tl) * ldq + (size_t)pair * dks + (mine ? at : 0), mine);
+            continue;
+        }
         cp_async16(Qs + r * LDK + c * 8, q + (size_t)(q0 + tl) * ldq + (size_t)((kvh * g + hg) * maps + map) * DK + c * 8, ok);
     }
     cp_async_commit();
@@ -136,7 +153,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         load_tile(stage0, stage0 + BN * LDK, kc, vc, tied != 0, table, kbeg, kend, kvh, Hkv, ps, num_pages, ldk, koff);
     cp_async_commit();
 
-    const int wrow = narrow ? 0 : warp;                    // the warp's 16 rows of the tile
+    const int wrow = NARROW ? 0 : warp;                    // the warp's 16 rows of the tile
     const int r_lo = wrow * 16 + (lane >> 2), r_hi = r_lo + 8;
     const int pos_lo = r_lo < nrows ? pos_base + (row0 + r_lo) / g : -1;
     const int pos_hi = r_hi < nrows ? pos_base + (row0 + r_hi) / g : -1;
@@ -145,13 +162,13 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     const int warp_pos_min = pos_base + (row0 + wrow * 16) / g;
     const int tig = lane & 3;
 
-    float o[NT_O][4];
+    float o[NO][4];
 #pragma unroll
-    for (int n = 0; n < NT_O; ++n)
+    for (int n = 0; n < NO; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    const bf16* Qw = Qs + wrow * 16 * LDK;
+    const bf16* Qw = Qs + wrow * 16 * LDK + ((lane & 15) & (q_rows - 1)) * LDK;   // this lane's row of the A tiles
 
     for (int t = 0; t < ntiles; ++t) {
         bf16* Ks = stage0 + (t & 1) * STAGE_ELEMS;
@@ -178,7 +195,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
             // (the fragment loads are issued one k-step ahead of the MMAs that use them: the
             // instructions keep their program order, so the order is written out here)
             unsigned af[2][4], bf[2][NT_S / 2][4];
-            ldmatrix_x4(af[0], Qw + (lane & 15) * LDK + (lane >> 4) * 8);
+            ldmatrix_x4(af[0], Qw + (lane >> 4) * 8);
 #pragma unroll
             for (int jp = 0; jp < NT_S / 2; ++jp)
                 ldmatrix_x4(bf[0][jp], Ks + (jp * 16 + (lane >> 4) * 8 + (lane & 7)) * LDK + ((lane >> 3) & 1) * 8);
@@ -186,7 +203,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
             for (int kk = 0; kk < KSTEPS; ++kk) {
                 const int cur = kk & 1, nxt = cur ^ 1;
                 if (kk + 1 < KSTEPS) {
-                    ldmatrix_x4(af[nxt], Qw + (lane & 15) * LDK + (kk + 1) * 16 + (lane >> 4) * 8);
+                    ldmatrix_x4(af[nxt], Qw + (kk + 1) * 16 + (lane >> 4) * 8);
 #pragma unroll
                     for (int jp = 0; jp < NT_S / 2; ++jp)
                         ldmatrix_x4(bf[nxt][jp], Ks + (jp * 16 + (lane >> 4) * 8 + (lane & 7)) * LDK + (kk + 1) * 16 +
@@ -230,7 +247,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
             }
             if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-                for (int n = 0; n < NT_O; ++n) {
+                for (int n = 0; n < NO; ++n) {
                     o[n][0] *= alpha[0];
                     o[n][1] *= alpha[0];
                     o[n][2] *= alpha[1];
@@ -246,27 +263,30 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
                 a[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
                 a[3] = pack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
                 unsigned vf[2][4];
-                if (narrow) {                              // this warp's share of the value columns
+                if constexpr (NARROW) {                    // this warp's share of the value columns
 #pragma unroll
-                    for (int np = 0; np < NT_O / 2; ++np) {
-                        if ((np & 3) == warp) {
-                            ldmatrix_x4_trans(vf[0], Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s +
-                                                         np * 16 + (lane >> 4) * 8);
-                            mma_bf16(o[2 * np], a, vf[0][0], vf[0][1]);
-                            mma_bf16(o[2 * np + 1], a, vf[0][2], vf[0][3]);
+                    for (int i = 0; i < NO / 2; ++i) {
+                        const int np = i * 4 + warp;
+                        if (np < NT_O / 2) {
+                            ldmatrix_x4_trans(vf[i & 1], Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s +
+                                                             np * 16 + (lane >> 4) * 8);
+                            mma_bf16(o[2 * i], a, vf[i & 1][0], vf[i & 1][1]);
+                            mma_bf16(o[2 * i + 1], a, vf[i & 1][2], vf[i & 1][3]);
                         }
                     }
                     continue;
                 }
-                ldmatrix_x4_trans(vf[0], Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s + (lane >> 4) * 8);
+                if constexpr (!NARROW) {
+                    ldmatrix_x4_trans(vf[0], Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s + (lane >> 4) * 8);
 #pragma unroll
-                for (int np = 0; np < NT_O / 2; ++np) {
-                    const int cur = np & 1, nxt = cur ^ 1;
-                    if (np + 1 < NT_O / 2)
-                        ldmatrix_x4_trans(vf[nxt], Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s +
-                                                       (np + 1) * 16 + (lane >> 4) * 8);
-                    mma_bf16(o[2 * np], a, vf[cur][0], vf[cur][1]);
-                    mma_bf16(o[2 * np + 1], a, vf[cur][2], vf[cur][3]);
+                    for (int np = 0; np < NT_O / 2; ++np) {
+                        const int cur = np & 1, nxt = cur ^ 1;
+                        if (np + 1 < NT_O / 2)
+                            ldmatrix_x4_trans(vf[nxt], Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s +
+                                                           (np + 1) * 16 + (lane >> 4) * 8);
+                        mma_bf16(o[2 * np], a, vf[cur][0], vf[cur][1]);
+                        mma_bf16(o[2 * np + 1], a, vf[cur][2], vf[cur][3]);
+                    }
                 }
             }
         }
@@ -289,15 +309,16 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         const int head = (kvh * g + hg) * maps + map;
         if (splits > 1) {
             const size_t pi = ((size_t)(q0 + tl) * H * maps + head) * splits + blockIdx.y;
-            if (tig == 0 && (!narrow || warp == 0)) {
+            if (tig == 0 && (!NARROW || warp == 0)) {
                 part_ml[2 * pi] = m[h];
                 part_ml[2 * pi + 1] = l[h];
             }
             float* po = part_o + pi * DV + tig * 2;
 #pragma unroll
-            for (int n = 0; n < NT_O; ++n)
-                if (!narrow || ((n >> 1) & 3) == warp)
-                    *reinterpret_cast<float2*>(po + n * 8) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+            for (int i = 0; i < NO; ++i) {
+                const int n = NARROW ? ((i >> 1) * 4 + warp) * 2 + (i & 1) : i;     // the tile's place in the row
+                if (n < NT_O) *reinterpret_cast<float2*>(po + n * 8) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+            }
             continue;
         }
         float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
@@ -308,16 +329,19 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         if (out_f32 != nullptr) {
             float* dst = out_f32 + (size_t)(q0 + tl) * ldo + (size_t)head * DV + tig * 2;
 #pragma unroll
-            for (int n = 0; n < NT_O; ++n)
-                if (!narrow || ((n >> 1) & 3) == warp)
-                    *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+            for (int i = 0; i < NO; ++i) {
+                const int n = NARROW ? ((i >> 1) * 4 + warp) * 2 + (i & 1) : i;
+                if (n < NT_O)
+                    *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+            }
             continue;
         }
         bf16* dst = out + (size_t)(q0 + tl) * ldo + (size_t)head * DV + tig * 2;
 #pragma unroll
-        for (int n = 0; n < NT_O; ++n)
-            if (!narrow || ((n >> 1) & 3) == warp)
-                *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+        for (int i = 0; i < NO; ++i) {
+            const int n = NARROW ? ((i >> 1) * 4 + warp) * 2 + (i & 1) : i;
+            if (n < NT_O) *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+        }
     }
 }
 
@@ -378,12 +402,24 @@ int slb_attention_kv_mma_status(int reset) {
     }
     return v;
 }
+// Blocks of the kernel an SM holds at once (separate keys and values), for the choice of splits:
+// `group` rows a tile in the narrow form.
+int slb_attention_kv_mma_resident(int narrow, int group) {
+    const int q_rows = narrow ? (group <= 8 ? 8 : 16) : BM;
+    const size_t smem = ((size_t)q_rows * LDK + 2 * stage_elems(false)) * sizeof(bf16);
+    int n = 0;
+    const cudaError_t e = narrow
+        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_kv_mma_kernel<true>, NTHREADS, smem)
+        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_kv_mma_kernel<false>, NTHREADS, smem);
+    return e == cudaSuccess && n > 0 ? n : 1;
+}
 static int launch_attention_kv_mma(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int tied, bf16* out,
                                    float* out_f32, int ldo, const int* block_table, int max_pages, const int* cu_q,
                                    const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
                                    int H, int Hkv, int maps, int ps, int num_pages, float scale, int window,
                                    const bf16* gate, int ldg, int splits, float* part_o, float* part_ml,
-                                   int narrow, cudaStream_t st) {
+                                   int narrow, int fold, cudaStream_t st) {
+    // `fold` > 1: H counts (head, map) pairs, `maps` is 1, DK is fold times a map's key size.
     // `narrow`: every tile of the list holds at most 16 rows (a step of single tokens with at most
     // 16 query heads a kv head).
     // `splits` > 1 (steps of single tokens only: a tile is one token's heads): scratch part_o
@@ -393,18 +429,24 @@ static int launch_attention_kv_mma(const bf16* q, int ldq, const bf16* kc, const
         return SLB_ERR_BAD_ARG;
     if (narrow && H / Hkv > 16) return SLB_ERR_BAD_ARG;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || scale <= 0.f ||
-        (tied && DV > DK) || ldq % 8 != 0 || ldo % 2 != 0 || maps < 1 || (maps > 1 && tied))
+        (tied && DV > DK) || ldq % 8 != 0 || ldo % 2 != 0 || maps < 1 || (maps > 1 && tied) || fold < 1 ||
+        (fold > 1 && (maps != 1 || tied || DK % (8 * fold) != 0 || H % fold != 0)))
         return SLB_ERR_BAD_ARG;
     if ((long long)num_tiles * Hkv * maps > 2147483647LL) return SLB_ERR_TOO_LARGE;
-    const size_t smem = ((size_t)(narrow ? 16 : BM) * LDK + 2 * stage_elems(tied != 0)) * sizeof(bf16);
-    static unsigned long long configured = 0;
-    const int rc = slb_configure(&configured, attention_kv_mma_kernel,
-                                 ((size_t)BM * LDK + 2 * stage_elems(false)) * sizeof(bf16));
+    // (a narrow tile of at most 8 rows keeps 8 rows of Q: a third block fits an SM at the largest sizes)
+    const int q_rows = narrow ? (H / Hkv <= 8 ? 8 : 16) : BM;
+    const size_t smem = ((size_t)q_rows * LDK + 2 * stage_elems(tied != 0)) * sizeof(bf16);
+    static unsigned long long configured = 0, configured_narrow = 0;
+    const int rc = narrow ? slb_configure(&configured_narrow, attention_kv_mma_kernel<true>,
+                                          ((size_t)16 * LDK + 2 * stage_elems(false)) * sizeof(bf16))
+                          : slb_configure(&configured, attention_kv_mma_kernel<false>,
+                                          ((size_t)BM * LDK + 2 * stage_elems(false)) * sizeof(bf16));
     if (rc != 0) return rc;
-    const int e = slb_launch(attention_kv_mma_kernel, dim3(num_tiles * Hkv * maps, splits), dim3(NTHREADS), smem, st,
+    const int e = slb_launch(narrow ? attention_kv_mma_kernel<true> : attention_kv_mma_kernel<false>,
+                             dim3(num_tiles * Hkv * maps, splits), dim3(NTHREADS), smem, st,
                              q, ldq, kc, tied ? kc : vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len,
                              tile_seq, tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window,
-                             gate, ldg, splits, part_o, part_ml, maps, out_f32, narrow ? 1 : 0);
+                             gate, ldg, splits, part_o, part_ml, maps, out_f32, q_rows, fold);
     if (e != 0 || splits == 1) return e;
     // (one tile a token: num_tiles is the number of tokens)
     return slb_launch(attention_kv_combine_kernel, dim3(num_tiles, H * maps), dim3(128), 0, st, (const float*)part_o,
@@ -419,7 +461,7 @@ int slb_attention_kv_mma_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
                               int narrow, cudaStream_t st) {
     return launch_attention_kv_mma(q, ldq, kc, vc, tied, out, nullptr, ldo, block_table, max_pages, cu_q, ctx_len,
                                    tile_seq, tile_row0, num_tiles, H, Hkv, 1, ps, num_pages, scale, window, gate,
-                                   ldg, splits, part_o, part_ml, narrow, st);
+                                   ldg, splits, part_o, part_ml, narrow, 1, st);
 }
 // `maps` attention maps a head; float32 results [token][head][map][DV] with rows `ldo` floats apart
 int slb_attention_kv_mma_maps_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int maps, float* out,
@@ -429,6 +471,18 @@ int slb_attention_kv_mma_maps_bf16(const bf16* q, int ldq, const bf16* kc, const
                                    float* part_o, float* part_ml, int narrow, cudaStream_t st) {
     return launch_attention_kv_mma(q, ldq, kc, vc, 0, nullptr, out, ldo, block_table, max_pages, cu_q, ctx_len,
                                    tile_seq, tile_row0, num_tiles, H, Hkv, maps, ps, num_pages, scale, window,
-                                   nullptr, 0, splits, part_o, part_ml, narrow, st);
+                                   nullptr, 0, splits, part_o, part_ml, narrow, 1, st);
+}
+// The same results from a library built for keys of maps * (a map's key size): the maps are rows
+// of one block (H and Hkv are the model's head counts; q [token][head][map][DK / maps]).
+int slb_attention_kv_mma_folded_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int maps, float* out,
+                                     int ldo, const int* block_table, int max_pages, const int* cu_q,
+                                     const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
+                                     int H, int Hkv, int ps, int num_pages, float scale, int window, int splits,
+                                     float* part_o, float* part_ml, int narrow, cudaStream_t st) {
+    if (maps < 1) return SLB_ERR_BAD_ARG;
+    return launch_attention_kv_mma(q, ldq, kc, vc, 0, nullptr, out, ldo, block_table, max_pages, cu_q, ctx_len,
+                                   tile_seq, tile_row0, num_tiles, H * maps, Hkv, 1, ps, num_pages, scale, window,
+                                   nullptr, 0, splits, part_o, part_ml, narrow, maps, st);
 }
 }

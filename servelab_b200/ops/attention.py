@@ -155,10 +155,12 @@ def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk,
 
 # ------------------------------------------------- several attention maps a head
 use_maps_tc = True         # steps with prompt portions: the tcgen05 kernel where it takes the sizes
-def prepare_maps_attention(key_dim: int, value_dim: int, dtype: torch.dtype) -> None:
+def prepare_maps_attention(key_dim: int, value_dim: int, dtype: torch.dtype, maps: int = 1, group: int = 1) -> None:
     """Builds what ``maps_attention`` will launch for these sizes (at load, not in a step)."""
     if _kv_fast(key_dim, value_dim, dtype) and torch.cuda.is_available():
         L.attention_kv(key_dim, value_dim)
+        if K.attention_kv_folds(group, maps, key_dim, value_dim):
+            L.attention_kv(maps * key_dim, value_dim)     # steps of single tokens
 
 
 def maps_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, maps, Dk, Dv, page_size, scale, window) -> None:

@@ -921,13 +921,31 @@ def attention_kv(ctx, q, k_cache, v_cache, v_row_stride: int, out, block_table, 
 
 
 def attention_kv_splits(num_seqs: int, num_kv_heads: int, longest_context: int, window: int,
-                        tile_keys: int = 64, max_splits: int = 32) -> int:
-    """Blocks a request's keys are split over in a step of single tokens: enough to fill the
-    device twice, at least two key tiles a block."""
+                        tile_keys: int = 64, max_splits: int = 32, resident: int = 2) -> int:
+    """Blocks a request's keys are split over in a step of single tokens.  With ``resident``
+    blocks an SM the step takes (waves of blocks) x (key tiles a block): the fewest splits with
+    the smallest such product, at least two key tiles a block."""
     seen = min(longest_context, window + tile_keys) if window > 0 else longest_context
     tiles = -(-seen // tile_keys)
-    want = -(-2 * _num_sms() // max(1, num_seqs * num_kv_heads))
-    return max(1, min(max_splits, want, tiles // 2))
+    units = max(1, num_seqs * num_kv_heads)
+    slots = max(1, _num_sms() * resident)
+    best, best_cost = 1, None
+    for s in range(1, max(1, min(max_splits, tiles // 2)) + 1):
+        cost = -(-units * s // slots) * -(-tiles // s)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
+
+
+_kv_resident = {}
+
+
+def attention_kv_resident(lib, k_dim: int, v_dim: int, narrow: bool, group: int) -> int:
+    """Blocks of the tensor-core kernel for these sizes that an SM holds at once."""
+    key = (k_dim, v_dim, bool(narrow), group <= 8)
+    if key not in _kv_resident:
+        _kv_resident[key] = int(lib.slb_attention_kv_mma_resident(1 if narrow else 0, group))
+    return _kv_resident[key]
 
 
 def attention_kv_mma(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num_heads: int,
@@ -941,8 +959,11 @@ def attention_kv_mma(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num
     tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads, rows)
     splits, part_o, part_ml = 1, None, None
     if ctx.decode_only and attention_kv_split and num_heads // num_kv_heads <= rows:
+        narrow = attention_kv_narrow and num_heads // num_kv_heads <= 16
         splits = attention_kv_splits(ctx.num_seqs, num_kv_heads, ctx.split_hint_len, window,
-                                     max_splits=lib.slb_attention_kv_mma_max_splits())
+                                     max_splits=lib.slb_attention_kv_mma_max_splits(),
+                                     resident=attention_kv_resident(lib, k_dim, v_dim, narrow,
+                                                                    num_heads // num_kv_heads))
         if splits > 1:
             T = q.shape[0]
             part_o = torch.empty((T, num_heads, splits, v_dim), dtype=_F32, device=q.device)
@@ -961,6 +982,20 @@ attention_kv_split = True      # (off: one block a request and kv head, the twin
 # steps of single tokens with at most 16 query heads a kv head: the block's warps share the rows
 # and split the value columns (off: a warp 16 rows, the twin)
 attention_kv_narrow = True
+
+
+# steps of single tokens with several maps a head: the maps become rows of one block (a library
+# built for keys of maps x the map's size), which reads a kv head's values once (off: a block a
+# map, the twin)
+attention_kv_fold = True
+ATTENTION_KV_FOLD_MAX_KEY = 320
+
+
+def attention_kv_folds(group: int, maps: int, k_dim: int, v_dim: int) -> bool:
+    """Whether a step of single tokens with ``maps`` maps a head and ``group`` heads a kv head
+    runs with the maps as rows of one block."""
+    return (attention_kv_fold and maps > 1 and group * maps <= 16 and k_dim % 8 == 0
+            and (maps * k_dim) % 16 == 0 and maps * k_dim <= ATTENTION_KV_FOLD_MAX_KEY and v_dim % 16 == 0)
 
 
 attention_kv_use_tc = True     # steps with prompt portions: the tcgen05 kernel where it takes the sizes
@@ -1282,13 +1317,38 @@ def attention_kv_mma_maps(ctx, q, k_cache, v_cache, out, block_table, num_heads:
     """The tensor-core kernel (bfloat16) with ``maps`` attention maps a head, layouts as
     ``attention_kv_maps``; in a step of single tokens the keys of a request are split over several
     blocks when the requests alone would not fill the device."""
+    if ctx.decode_only and attention_kv_folds(num_heads // num_kv_heads, maps, k_dim, v_dim):
+        # a step of single tokens: the maps are rows of one block, which reads the values once
+        lib = L.attention_kv(maps * k_dim, v_dim)
+        group = num_heads // num_kv_heads * maps
+        tile_seq, tile_row0, n = ctx.attention_tiles(group, lib.slb_attention_kv_mma_tile_rows())
+        splits, part_o, part_ml = 1, None, None
+        if attention_kv_split:
+            splits = attention_kv_splits(ctx.num_seqs, num_kv_heads, ctx.split_hint_len, window,
+                                         max_splits=lib.slb_attention_kv_mma_max_splits(),
+                                         resident=attention_kv_resident(lib, maps * k_dim, v_dim,
+                                                                        attention_kv_narrow, group))
+            if splits > 1:
+                T = q.shape[0]
+                part_o = torch.empty((T, num_heads * maps, splits, v_dim), dtype=_F32, device=q.device)
+                part_ml = torch.empty((T, num_heads * maps, splits, 2), dtype=_F32, device=q.device)
+        L.check(lib.slb_attention_kv_mma_folded_bf16(
+            q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), maps, out.data_ptr(), out.stride(0),
+            block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_len.data_ptr(),
+            tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads, page_size, k_cache.shape[0],
+            float(scale), int(window), splits, _p(part_o), _p(part_ml), 1 if attention_kv_narrow else 0,
+            _stream()), "attention_kv_mma")
+        return
     lib = L.attention_kv(k_dim, v_dim)
     rows = lib.slb_attention_kv_mma_tile_rows()
     tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads, rows)
     splits, part_o, part_ml = 1, None, None
     if ctx.decode_only and attention_kv_split and num_heads // num_kv_heads <= rows:
         splits = attention_kv_splits(ctx.num_seqs, num_kv_heads * maps, ctx.split_hint_len, window,
-                                     max_splits=lib.slb_attention_kv_mma_max_splits())
+                                     max_splits=lib.slb_attention_kv_mma_max_splits(),
+                                     resident=attention_kv_resident(
+                                         lib, k_dim, v_dim, attention_kv_narrow and num_heads // num_kv_heads <= 16,
+                                         num_heads // num_kv_heads))
         if splits > 1:
             T = q.shape[0]
             part_o = torch.empty((T, num_heads * maps, splits, v_dim), dtype=_F32, device=q.device)

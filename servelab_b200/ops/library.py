@@ -258,7 +258,9 @@ _ATTN_KV_SIGNATURES = {
     "slb_attention_kv_mma_status": [I],
     "slb_attention_kv_mma_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P, I, I, P, P, I, P],
     "slb_attention_kv_mma_max_splits": [],
+    "slb_attention_kv_mma_resident": [I, I],
     "slb_attention_kv_mma_maps_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P, P, I, P],
+    "slb_attention_kv_mma_folded_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P, P, I, P],
     "slb_attention_kv_tc_supported": [I, I, I],
     "slb_attention_kv_tc_tile_rows": [I],
     "slb_attention_kv_tc_status": [I],

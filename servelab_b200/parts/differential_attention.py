@@ -44,7 +44,7 @@ class DifferentialAttention(Mixer):
         self.k_size = s.num_kv_heads * self.MAPS * s.head_dim
         self.v_size = s.num_kv_heads * s.value_dim
         A.check_kv_supported(s.head_dim, s.value_dim)
-        A.prepare_maps_attention(s.head_dim, s.value_dim, env.dtype)
+        A.prepare_maps_attention(s.head_dim, s.value_dim, env.dtype, maps=2, group=s.num_heads // s.num_kv_heads)
 
     @classmethod
     def _names(cls, spec, prefix):

@@ -248,7 +248,7 @@ def _run_decay_steps(K, proj, decay, state, Hh, D, Dv, pieces, act, rot, key_sca
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(3, 8, 12, None, None), (2, 16, 8, None, (500.0, 8)), (1, 24, 40, "silu", None),
                                    (2, 64, 64, None, (10000.0, 64)), (3, 10, 6, "silu", (900.0, 4)),
-                                   (2, 128, 96, "silu", None), (1, 256, 33, None, (1e6, 128))])
+                                   (2, 128, 96, "silu", None), (1, 256, 33, None, (2e5, 128))])
 def test_decay_attention_whole_in_portions_and_token_by_token(dtype, shape):
     """Three requests of unequal length in one batch, against the closed form; then the same cut
     into portions (down to two tokens and one) with the state carried in slots, which must give
@@ -299,7 +299,7 @@ def test_decay_attention_keeps_a_key_from_far_back():
 @pytest.mark.parametrize("split", [True, False])
 @pytest.mark.parametrize("shape", [(3, 8, 12, None, None), (2, 16, 8, None, (500.0, 8)), (1, 24, 40, "silu", None),
                                    (2, 64, 64, None, (10000.0, 64)), (3, 10, 6, "silu", (900.0, 4)),
-                                   (2, 128, 96, "silu", None), (1, 128, 130, None, (1e6, 64)),
+                                   (2, 128, 96, "silu", None), (1, 128, 130, None, (2e5, 64)),
                                    (2, 48, 64, None, (300.0, 48))])
 def test_decay_attention_in_chunks_on_the_tensor_cores(shape, split):
     """The chunked kernels against the closed form: requests of unequal length (shorter than a
@@ -389,7 +389,7 @@ def _maps_case(seed, Hq, G, D, Dv, ctxs, qlens, ps, dtype, spike=None):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, "plain twin", "mma.sync twin"])
-@pytest.mark.parametrize("shape", [(4, 2, 16, 8, 8), (3, 3, 10, 6, 4), (4, 1, 64, 128, 16), (2, 1, 48, 96, 16),
+@pytest.mark.parametrize("shape", [(4, 2, 16, 8, 8), (3, 3, 10, 6, 4), (4, 1, 64, 128, 16), (2, 1, 48, 80, 16),
                                    (6, 3, 32, 16, 8), (6, 2, 128, 128, 16), (4, 4, 128, 64, 8)])
 @pytest.mark.parametrize("spike", [None, 0, 1, 33, 290])
 def test_attention_with_two_maps(dtype, shape, spike, monkeypatch):
@@ -423,18 +423,21 @@ def test_attention_with_two_maps(dtype, shape, spike, monkeypatch):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(4, 1, 64, 128, 16), (4, 2, 48, 96, 32), (3, 3, 10, 6, 4), (8, 2, 128, 256, 16),
-                                   (40, 2, 32, 48, 8)])
-@pytest.mark.parametrize("narrow", [True, False])
-def test_attention_with_two_maps_single_tokens_at_long_contexts(dtype, shape, narrow, monkeypatch):
+@pytest.mark.parametrize("shape", [(4, 1, 64, 128, 16), (4, 2, 80, 48, 32), (3, 3, 10, 6, 4), (8, 2, 128, 256, 16),
+                                   (40, 2, 32, 48, 8), (8, 1, 16, 32, 8), (6, 2, 24, 16, 4)])
+@pytest.mark.parametrize("mode", ["fold", "narrow", "wide"])
+def test_attention_with_two_maps_single_tokens_at_long_contexts(dtype, shape, mode, monkeypatch):
     """A step of single tokens only (few requests, long contexts: the tensor-core kernel splits the
-    keys over blocks), with a dominant key 900 tokens back in the second map.  ``narrow``: the
-    warps of a block share the (at most 16) rows and split the value columns; off, and with more
-    than 16 heads a kv head: a warp 16 rows."""
+    keys over blocks), with a dominant key 900 tokens back in the second map.  ``fold``: the maps
+    of a kv head are rows of one block (at most 16 rows with both maps, else as ``narrow``);
+    ``narrow``: a block a map, its warps share the (at most 16) rows and split the value columns;
+    ``wide``, and with more than 16 heads a kv head: a warp 16 rows."""
     from servelab_b200.ops import attention as A
     from servelab_b200.ops import kernels as K
-    monkeypatch.setattr(K, "attention_kv_narrow", narrow)
+    monkeypatch.setattr(K, "attention_kv_fold", mode == "fold")
+    monkeypatch.setattr(K, "attention_kv_narrow", mode != "wide")
     Hq, G, D, Dv, ps = shape
+    assert K.attention_kv_folds(Hq // G, 2, D, Dv) == (mode == "fold" and Hq // G <= 8 and D % 8 == 0 and Dv % 16 == 0)
     ctxs, qlens = [1400, 901, 1000], [1, 1, 1]
     q, kc, vc, want, entries = _maps_case(5 + D, Hq, G, D, Dv, ctxs, qlens, ps, dtype, 900)
     ctx = _ctx(entries)
@@ -442,7 +445,7 @@ def test_attention_with_two_maps_single_tokens_at_long_contexts(dtype, shape, na
     if dtype == torch.bfloat16 and D % 16 == 0:
         assert K.attention_kv_splits(3, G * 2, 1400, 0) > 1
     out = torch.empty(3, Hq * 2 * Dv, dtype=torch.float32, device=DEV)
-    A.prepare_maps_attention(D, Dv, dtype)
+    A.prepare_maps_attention(D, Dv, dtype, maps=2, group=Hq // G)
     A.maps_attention(ctx, q.to(DEV), kc.to(DEV), vc.to(DEV), out, ctx.block_tables[0], Hq, G, 2, D, Dv, ps, 0.3, 0)
     tol = 3e-5 if dtype == torch.float32 else 3e-2
     assert (out.cpu().double() - want).abs().max() < tol * max(1.0, float(want.abs().max()))
