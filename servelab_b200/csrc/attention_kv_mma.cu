@@ -407,6 +407,12 @@ int slb_attention_kv_mma_status(int reset) {
 int slb_attention_kv_mma_resident(int narrow, int group) {
     const int q_rows = narrow ? (group <= 8 ? 8 : 16) : BM;
     const size_t smem = ((size_t)q_rows * LDK + 2 * stage_elems(false)) * sizeof(bf16);
+    static unsigned long long configured = 0, configured_narrow = 0;       // (sizes above 48 KB need the opt-in first)
+    const int rc = narrow ? slb_configure(&configured_narrow, attention_kv_mma_kernel<true>,
+                                          ((size_t)16 * LDK + 2 * stage_elems(false)) * sizeof(bf16))
+                          : slb_configure(&configured, attention_kv_mma_kernel<false>,
+                                          ((size_t)BM * LDK + 2 * stage_elems(false)) * sizeof(bf16));
+    if (rc != 0) return 1;
     int n = 0;
     const cudaError_t e = narrow
         ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_kv_mma_kernel<true>, NTHREADS, smem)
