@@ -457,7 +457,7 @@ LENGTHS = [70, 45, 190, 33, 2, 1, 58]
 TOL = {"float32": 5e-5, "bfloat16": 3e-2}       # of the largest logit
 
 
-@pytest.fixture(scope="module", params=["P", "Q", "R", "S"])
+@pytest.fixture(scope="module", params=["P", "Q", "R", "S", "T"])
 def model(request, tmp_path_factory):
     cfg, seed, page = C.CASES[request.param]
     folder = C.make_model(str(tmp_path_factory.mktemp(f"zim_{request.param}")), cfg, seed)

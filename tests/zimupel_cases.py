@@ -72,7 +72,16 @@ S = {"architecture": "Zimupel", "vocab": 150, "width": 128, "norm": {"eps": 1e-5
                 layer(attention(4, 1, 64, 128, 0.125, 0.6), dense(64)),
                 layer(lightning(2, 128, 64, (0.96, 0.999)), moe(8, 4, 16, (2, 1))),
                 layer(attention(4, 1, 64, 128, 0.1, 0.28, kv_from=1), moe(4, 1, 48))]}
-CASES = {"P": (P, 5, 8), "Q": (Q, 9, 16), "R": (R, 13, 4), "S": (S, 17, 16)}        # config, seed, page size
+# sizes in multiples of 16 but not of 64 (the mma.sync attention in prompts, the maps as rows of one
+# block in single tokens), attention first, three groups of experts, two cache readers of one layer
+T = {"architecture": "Zimupel", "vocab": 320, "width": 192, "norm": {"eps": 1e-6}, "streams": 2,
+     "logit_scale": 3.0, "logit_softcap": 40.0,
+     "layers": [layer(attention(6, 3, 32, 64, 0.15, 0.45), dense(80)),
+                layer(lightning(3, 48, 48, (0.9, 0.97, 0.999)), moe(6, 2, 40, (3, 1))),
+                layer(attention(6, 3, 32, 64, 0.2, 0.15, kv_from=0), dense(64)),
+                layer(retention(4, 32, 80, (0.95, 0.99, 0.995, 0.9995), rot=(50000.0, 16)), moe(12, 3, 24, (3, 2))),
+                layer(attention(12, 3, 32, 64, 0.17, 0.7, kv_from=0), None)]}
+CASES = {"P": (P, 5, 8), "Q": (Q, 9, 16), "R": (R, 13, 4), "S": (S, 17, 16), "T": (T, 21, 32)}   # config, seed, page size
 # projections drawn large enough that the softmax of a tiny model is peaked and the router's
 # choice is clear of ties
 STD_OF = {"embed": 0.5, ".mix.q": 0.3, ".mix.k": 0.3, ".router": 0.4, ".correction": 0.3, ".hc": 0.5,
