@@ -424,7 +424,8 @@ def test_attention_with_two_maps(dtype, shape, spike, monkeypatch):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(4, 1, 64, 128, 16), (4, 2, 80, 48, 32), (3, 3, 10, 6, 4), (8, 2, 128, 256, 16),
-                                   (40, 2, 32, 48, 8), (8, 1, 16, 32, 8), (6, 2, 24, 16, 4)])
+                                   (40, 2, 32, 48, 8), (8, 1, 16, 32, 8), (6, 2, 24, 16, 4), (2, 2, 32, 32, 8),
+                                   (5, 1, 16, 16, 8), (14, 2, 16, 32, 16)])
 @pytest.mark.parametrize("mode", ["fold", "narrow", "wide"])
 def test_attention_with_two_maps_single_tokens_at_long_contexts(dtype, shape, mode, monkeypatch):
     """A step of single tokens only (few requests, long contexts: the tensor-core kernel splits the
