@@ -25,10 +25,11 @@
 #define DA_PARTS 8
 #define DA_TT 8
 #define DA_MAX_D 256
-#define DA_R (DA_MAX_D / DA_PARTS)
 
-template <typename T>
-__global__ void __launch_bounds__(DA_EV * DA_PARTS) decay_attention_kernel(const DecayAttnArgs a) {
+// R: state rows a thread holds (head size / DA_PARTS, rounded up to 16 or 32): with 16 the kernel
+// fits 64 registers, so four blocks an SM keep their state slices in flight.
+template <typename T, int R>
+__global__ void __launch_bounds__(DA_EV * DA_PARTS, R <= 16 ? 4 : 2) decay_attention_kernel(const DecayAttnArgs a) {
     extern __shared__ float da_smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -52,9 +53,9 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS) decay_attention_kernel(const
     const float dec = a.decay[h];
     float* srow = a.state + ((size_t)slot * a.H + h) * (size_t)D * Dv;
 
-    float st[DA_R];
+    float st[R];
 #pragma unroll
-    for (int i = 0; i < DA_R; ++i) {
+    for (int i = 0; i < R; ++i) {
         const int d = p * Dp + i;
         st[i] = (live && i < Dp && d < D) ? srow[(size_t)d * Dv + col] : 0.f;
     }
@@ -91,7 +92,7 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS) decay_attention_kernel(const
             const float4* kj = reinterpret_cast<const float4*>(ks + j * LD + p * Dpad);
             float acc = 0.f;
 #pragma unroll
-            for (int i4 = 0; i4 < DA_R / 4; ++i4) {
+            for (int i4 = 0; i4 < R / 4; ++i4) {
                 if (i4 * 4 < Dp) {                         // (the same for every thread)
                     const float4 k4 = kj[i4], q4 = qj[i4];
                     st[4 * i4] = fmaf(dec, st[4 * i4], k4.x * v);
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS) decay_attention_kernel(const
         // before the second barrier; `part` is written again only after the next first barrier)
     }
 #pragma unroll
-    for (int i = 0; i < DA_R; ++i) {
+    for (int i = 0; i < R; ++i) {
         const int d = p * Dp + i;
         if (live && i < Dp && d < D) srow[(size_t)d * Dv + col] = st[i];
     }
@@ -137,7 +138,10 @@ static int launch_decay_attention(const DecayAttnArgs* a, int num_seqs, cudaStre
     if (vz > 65535) return SLB_ERR_TOO_LARGE;
     const int dpad = ((a->D + DA_PARTS - 1) / DA_PARTS + 3) / 4 * 4;
     const size_t smem = ((size_t)2 * DA_TT * DA_PARTS * dpad + DA_TT * DA_EV + DA_TT * DA_PARTS * DA_EV) * sizeof(float);
-    return slb_launch(decay_attention_kernel<T>, dim3(num_seqs, a->H, vz), dim3(DA_EV * DA_PARTS), smem, st, *a);
+    if (a->D <= 16 * DA_PARTS)
+        return slb_launch(decay_attention_kernel<T, 16>, dim3(num_seqs, a->H, vz), dim3(DA_EV * DA_PARTS), smem, st, *a);
+    return slb_launch(decay_attention_kernel<T, DA_MAX_D / DA_PARTS>, dim3(num_seqs, a->H, vz), dim3(DA_EV * DA_PARTS),
+                      smem, st, *a);
 }
 
 extern "C" {
