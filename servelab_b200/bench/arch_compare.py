@@ -180,7 +180,7 @@ ZIMUPEL_SIZES = {
 def zimupel_config(width, heads, kv, dim, experts, groups, keep, top, eff, streams, layers=LAYERS) -> dict:
     mlp = {"kind": "moe", "expert": {"ff": eff},
            "router": {"experts": experts, "groups": {"count": groups, "keep": keep}, "top": top}}
-    decay = [1.0 - 2.0 ** (-5 - 0.5 * i) for i in range(heads)]
+    decay = [1.0 - 2.0 ** (-4.75 - 0.5 * i) for i in range(heads)]
     ret = {"heads": heads, "dim": dim, "vdim": dim, "decay": decay, "rot": {"base": 500000.0, "dims": dim}}
     lig = {"heads": heads, "dim": dim, "vdim": dim, "decay": decay}
     att = {"heads": heads // 2, "kv_heads": max(1, kv // 2), "dim": dim, "vdim": 2 * dim, "scale": dim ** -0.5,
