@@ -34,6 +34,16 @@ class RotarySpec(PartSpec):
     head_dim: int = 0
     rotary_dim: int = 0
     theta: float = 10000.0
+    # Stretching of the long wavelengths (None: none): with wavelength l = 2 pi / f, a frequency
+    # with l > stretch_original / stretch_low is divided by ``stretch_factor``, one with
+    # l < stretch_original / stretch_high is kept, and between the two
+    # s = (stretch_original / l - stretch_low) / (stretch_high - stretch_low) blends them,
+    # (1 - s) f / factor + s f.
+    stretch_factor: Optional[float] = None
+    stretch_low: float = 1.0
+    stretch_high: float = 4.0
+    stretch_original: float = 8192.0
+    precise: bool = False      # the frequencies are formed in float64 and rounded to float32 once
 
 
 @dataclass(frozen=True)
@@ -55,6 +65,11 @@ class PairRotarySpec(PartSpec):
     yarn_original: float = 0.0
     yarn_fast: float = 32.0
     yarn_slow: float = 1.0
+    # stretching of the long wavelengths as ``RotarySpec`` describes it (None: none)
+    stretch_factor: Optional[float] = None
+    stretch_low: float = 1.0
+    stretch_high: float = 4.0
+    stretch_original: float = 8192.0
 
 
 # --------------------------------------------------------------------- norms
@@ -64,6 +79,7 @@ class RMSNormSpec(PartSpec):
     dim: int = 0
     eps: float = 1e-6
     weight_suffix: str = ".weight"         # the weight is <prefix><weight_suffix>
+    unit_offset: bool = False              # the stored weight lies around zero: the factor is 1 + w
 
 
 @dataclass(frozen=True)
@@ -167,9 +183,18 @@ class NormedAttentionSpec(PartSpec):
     """Grouped-query softmax attention whose keys and values may differ in size, with these
     steps, each a parameter:
 
+    ``conv_taps``    a causal convolution over time on every channel of the projected queries,
+                     keys and values, directly after the projection (0: none); the last
+                     ``conv_taps - 1`` projected rows of a request are per-request state;
     ``qk_norm``      RMS norm over every query and key head before the rotation, one weight
                      vector per projection shared by the heads (``qk_norm_eps``);
-    ``position``     a ``PairRotarySpec`` on the first ``dims`` elements of a head, or none;
+    ``position``     a ``PairRotarySpec`` (neighbouring pairs) or a ``RotarySpec`` (element i with
+                     element i + dims / 2) on the first ``dims`` elements of a head, or none;
+    ``qk_unit_norm`` after the rotation every query and key head is divided by its root mean
+                     square (``qk_norm_eps``, no weight);
+    ``softcap``      a scaled score s becomes cap tanh(s / cap) (None: not applied);
+    ``sink``         one learned number a head whose exponential joins the softmax's denominator
+                     (it has no key and no value, is neither scaled nor capped);
     ``value_mix``    None; "source": this layer's values (before any mixing) are kept for the
                      step; "mix": v <- (1 - lambda) v + lambda v_source with a learned scalar,
                      the mixed values being what the cache holds.  ``value_mix_key`` names the
@@ -191,6 +216,10 @@ class NormedAttentionSpec(PartSpec):
     value_mix: Optional[str] = None
     value_mix_key: str = "v_first"
     head_gate: bool = False
+    conv_taps: int = 0
+    qk_unit_norm: bool = False
+    softcap: Optional[float] = None
+    sink: bool = False
     q_name: str = "q"
     k_name: str = "k"
     v_name: str = "v"
@@ -199,6 +228,8 @@ class NormedAttentionSpec(PartSpec):
     q_norm_name: str = "q.norm"
     k_norm_name: str = "k.norm"
     value_mix_name: str = "vmix"
+    conv_suffix: str = ".conv"             # the taps of a projection: <projection><conv_suffix>
+    sink_name: str = "sink"
 
 
 @dataclass(frozen=True)
@@ -208,7 +239,10 @@ class LatentAttentionSpec(PartSpec):
     ``rope_dim`` elements of a rotated key part that all heads share; head h's unrotated key is
     W_uk[h] c and its value W_uv[h] c.  A query head is [``head_dim`` unrotated | ``rope_dim``
     rotated].  Only the latent and the rotated part are cached.  ``element_gate``: the
-    concatenated heads are multiplied by sigmoid(W_g x)."""
+    concatenated heads are multiplied by sigmoid(W_g x); ``head_gate``: head h's result by
+    sigmoid((W_g x)_h), one number a head.  ``q_rank``: the queries come through a latent of
+    their own, q = W_uq RMSnorm(W_dq x) (None: q = W_q x).  ``sink``: one learned number a head
+    whose exponential joins the softmax's denominator."""
     kind: str = "latent_attention"
     hidden_size: int = 0
     num_heads: int = 0
@@ -221,6 +255,13 @@ class LatentAttentionSpec(PartSpec):
     latent_norm_eps: float = 1e-6
     position: PartSpec = field(default_factory=NoPositionSpec)
     element_gate: bool = False
+    head_gate: bool = False
+    q_rank: Optional[int] = None
+    sink: bool = False
+    q_down_name: str = "dq"
+    q_norm_name: str = "dq.norm"
+    q_up_name: str = "uq"
+    sink_name: str = "sink"
     q_name: str = "q"
     down_name: str = "dkv"
     latent_norm_name: str = "dkv.norm"
@@ -244,6 +285,13 @@ class DecayAttentionSpec(PartSpec):
                         "row": the concatenated heads are RMS-normed together;
                         with ``out_norm_weight`` a learned weight over the whole row multiplies;
     ``gate_activation`` the result is multiplied by act(W_g x): "silu" or "sigmoid".
+
+    ``decay_gate_rank``: instead of the fixed ``decay`` (then empty) every key channel of every
+    token has a decay of its own, alpha_t = sigmoid(z_t)^(1 / ``decay_gate_tau``) with
+    z = W_a2 (W_a1 x) + b through a bottleneck of that many elements, and
+    S_t = diag(alpha_t) S_{t-1} + k_t v_t^T.  ``query_scale``: a factor on the queries (None: 1).
+    ``out_norm_per_head``: with ``out_norm`` "head" and a weight, the weight has ``value_dim``
+    elements and is shared by the heads.
     """
     kind: str = "decay_attention"
     hidden_size: int = 0
@@ -258,12 +306,19 @@ class DecayAttentionSpec(PartSpec):
     out_norm_weight: bool = False
     out_norm_eps: float = 1e-6
     gate_activation: str = "silu"
+    decay_gate_rank: Optional[int] = None
+    decay_gate_tau: float = 1.0
+    query_scale: Optional[float] = None
+    out_norm_per_head: bool = False
     q_name: str = "q"
     k_name: str = "k"
     v_name: str = "v"
     gate_name: str = "g"
     o_name: str = "o"
     out_norm_name: str = "norm"
+    decay_down_name: str = "a1"
+    decay_up_name: str = "a2"
+    decay_bias_name: str = "a2.b"
 
 
 @dataclass(frozen=True)
@@ -296,15 +351,35 @@ class DifferentialAttentionSpec(PartSpec):
     lambda_names: Tuple[str, str, str, str] = ("lq1", "lk1", "lq2", "lk2")
 
 
+@dataclass(frozen=True)
+class ParallelMixersSpec(PartSpec):
+    """Two mixers side by side that read the same input; each one's result is RMS-normed over the
+    model width with a weight of its own (``eps``) and the mixer returns ``factor`` times their
+    sum.  The branches' tensors live under ``<prefix>.<left_name>`` and ``<prefix>.<right_name>``,
+    the norm weights under ``<prefix>.<left_name><out_suffix>`` and the same for the right."""
+    kind: str = "parallel_mixers"
+    hidden_size: int = 0
+    left: PartSpec = None
+    right: PartSpec = None
+    eps: float = 1e-6
+    factor: float = 0.5
+    left_name: str = "left"
+    right_name: str = "right"
+    out_suffix: str = ".out"
+
+
 # -------------------------------------------------------------- feed-forward
 @dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
     """down(act(gate(x)) * up(x)) with a dense (expert-free) gate/up/down; ``activation``
-    "silu" or "gelu_tanh"."""
+    "silu", "gelu_tanh" or "swish_clamped": g = min(gate, limit), u = clamp(up, -limit, limit),
+    g sigmoid(``swish_alpha`` g) (u + 1)."""
     kind: str = "gated_mlp"
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
+    limit: Optional[float] = None          # (swish_clamped)
+    swish_alpha: float = 1.702
     bias: bool = False
     gate_name: str = "gate_proj"           # checkpoint names under the feed-forward's prefix
     up_name: str = "up_proj"

@@ -11,6 +11,10 @@
 // Optional epilogue: the row of head h is multiplied by sigmoid(gate[token][h]) (one number a
 // head).
 //
+// Optional in the scores: a soft cap, s <- cap tanh(s / cap) on the scaled score (`softcap` > 0),
+// and a sink, one number a head whose exponential is added to the softmax's denominator once (it
+// has no key and no value and is neither scaled nor capped).
+//
 // Several attention maps a head (`maps`, the differential form): every query head and every kv
 // head carries `maps` query / key vectors side by side ([head][map][Dk], key rows `ldk` apart),
 // each map is an attention of its own over the kv head's one set of values, and the results are
@@ -41,7 +45,7 @@ __global__ void __launch_bounds__(AK_THREADS) attention_kv_kernel(
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
     int H, int Hkv, int Dk, int Dv, int ps, int num_pages, float scale, int window,
-    const T* __restrict__ gate, int ldg) {
+    const T* __restrict__ gate, int ldg, float softcap, const float* __restrict__ sink) {
     extern __shared__ float ak_smem[];
     pdl_wait();
     const int ldq_s = Dk + 1;
@@ -131,7 +135,9 @@ __global__ void __launch_bounds__(AK_THREADS) attention_kv_kernel(
         for (int j = 0; j < 4; ++j) {
             const int kp = k0 + c0 + 8 * j;
             const bool vis = row_valid && kp <= my_pos && (window <= 0 || my_pos - kp < window);
-            sc[j] = vis ? sc[j] * scale : -INFINITY;
+            float sv = sc[j] * scale;
+            if (softcap > 0.f) sv = softcap * tanhf(sv / softcap);
+            sc[j] = vis ? sv : -INFINITY;
             tmax = fmaxf(tmax, sc[j]);
         }
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
@@ -187,6 +193,7 @@ __global__ void __launch_bounds__(AK_THREADS) attention_kv_kernel(
         const int rho = row0 + r;
         const int tl = rho / g, hg = rho - tl * g;
         const int head = (kvh * g + hg) * maps + map;
+        if (sink != nullptr) l += (m == -INFINITY) ? 1.f : expf(sink[head] - m);
         float inv = l > 0.f ? 1.0f / l : 0.f;
         if (gate != nullptr) {
             const float z = to_float(gate[(size_t)(q0 + tl) * ldg + head]);
@@ -208,8 +215,10 @@ static int launch_attention_kv(const T* q, int ldq, const T* kc, int ldk, int ma
                                const int* block_table, int max_pages, const int* cu_q,
                                const int* ctx_len, const int* tile_seq, const int* tile_row0,
                                int num_tiles, int H, int Hkv, int Dk, int Dv, int ps, int num_pages,
-                               float scale, int window, const T* gate, int ldg, cudaStream_t st) {
+                               float scale, int window, const T* gate, int ldg, float softcap,
+                               const float* sink, cudaStream_t st) {
     if (num_tiles <= 0) return 0;
+    if (softcap < 0.f || (sink != nullptr && maps != 1)) return SLB_ERR_BAD_ARG;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || Dk <= 0 || Dv <= 0 || ps <= 0 || max_pages <= 0 ||
         num_pages <= 0 || ldv < Dv || maps <= 0 || ldk < maps * Dk)
         return SLB_ERR_BAD_ARG;
@@ -222,7 +231,7 @@ static int launch_attention_kv(const T* q, int ldq, const T* kc, int ldk, int ma
     if (rc != 0) return rc;
     return slb_launch(attention_kv_kernel<T, TO>, dim3(num_tiles, Hkv * maps), dim3(AK_THREADS), smem, st, q, ldq,
                       kc, ldk, maps, vc, ldv, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq, tile_row0,
-                      H, Hkv, Dk, Dv, ps, num_pages, scale, window, gate, ldg);
+                      H, Hkv, Dk, Dv, ps, num_pages, scale, window, gate, ldg, softcap, sink);
 }
 
 extern "C" {
@@ -231,19 +240,19 @@ int slb_attention_kv_f32(const float* q, int ldq, const float* kc, const float* 
                          int ldo, const int* block_table, int max_pages, const int* cu_q,
                          const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
                          int H, int Hkv, int Dk, int Dv, int ps, int num_pages, float scale, int window,
-                         const float* gate, int ldg, cudaStream_t st) {
+                         const float* gate, int ldg, float softcap, const float* sink, cudaStream_t st) {
     return launch_attention_kv<float, float>(q, ldq, kc, Dk, 1, vc, ldv, out, ldo, block_table, max_pages, cu_q,
                                       ctx_len, tile_seq, tile_row0, num_tiles, H, Hkv, Dk, Dv, ps,
-                                      num_pages, scale, window, gate, ldg, st);
+                                      num_pages, scale, window, gate, ldg, softcap, sink, st);
 }
 int slb_attention_kv_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int ldv, bf16* out,
                           int ldo, const int* block_table, int max_pages, const int* cu_q,
                           const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
                           int H, int Hkv, int Dk, int Dv, int ps, int num_pages, float scale, int window,
-                          const bf16* gate, int ldg, cudaStream_t st) {
+                          const bf16* gate, int ldg, float softcap, const float* sink, cudaStream_t st) {
     return launch_attention_kv<bf16, bf16>(q, ldq, kc, Dk, 1, vc, ldv, out, ldo, block_table, max_pages, cu_q,
                                      ctx_len, tile_seq, tile_row0, num_tiles, H, Hkv, Dk, Dv, ps,
-                                     num_pages, scale, window, gate, ldg, st);
+                                     num_pages, scale, window, gate, ldg, softcap, sink, st);
 }
 // several maps a head (see the top of the file); the results are float32 in both forms
 int slb_attention_kv_maps_f32(const float* q, int ldq, const float* kc, int ldk, int maps, const float* vc, int ldv,
@@ -253,7 +262,7 @@ int slb_attention_kv_maps_f32(const float* q, int ldq, const float* kc, int ldk,
                               cudaStream_t st) {
     return launch_attention_kv<float, float>(q, ldq, kc, ldk, maps, vc, ldv, out, ldo, block_table, max_pages, cu_q,
                                              ctx_len, tile_seq, tile_row0, num_tiles, H, Hkv, Dk, Dv, ps,
-                                             num_pages, scale, window, nullptr, 0, st);
+                                             num_pages, scale, window, nullptr, 0, 0.f, nullptr, st);
 }
 int slb_attention_kv_maps_bf16(const bf16* q, int ldq, const bf16* kc, int ldk, int maps, const bf16* vc, int ldv,
                                float* out, int ldo, const int* block_table, int max_pages, const int* cu_q,
@@ -262,6 +271,6 @@ int slb_attention_kv_maps_bf16(const bf16* q, int ldq, const bf16* kc, int ldk, 
                                cudaStream_t st) {
     return launch_attention_kv<bf16, float>(q, ldq, kc, ldk, maps, vc, ldv, out, ldo, block_table, max_pages, cu_q,
                                             ctx_len, tile_seq, tile_row0, num_tiles, H, Hkv, Dk, Dv, ps,
-                                            num_pages, scale, window, nullptr, 0, st);
+                                            num_pages, scale, window, nullptr, 0, 0.f, nullptr, st);
 }
 }

@@ -96,7 +96,11 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
     const int* __restrict__ tile_row0, int H, int Hkv, int ps, int num_pages, float scale_log2,
     int window, const bf16* __restrict__ gate, int ldg, int splits, float* __restrict__ part_o,
-    float* __restrict__ part_ml, int maps, float* __restrict__ out_f32, int q_rows, int fold) {
+    float* __restrict__ part_ml, int maps, float* __restrict__ out_f32, int q_rows, int fold,
+    float softcap, float scale, const float* __restrict__ sink) {
+    // softcap > 0: a scaled score s becomes softcap tanh(s / softcap); sink: one number a head whose
+    // exponential joins the softmax's denominator (added where the row is finished: here without
+    // key splits, in the combine kernel with them)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
     constexpr int NO = NARROW ? ((NT_O / 2 + 3) / 4) * 2 : NT_O;      // 8-column tiles of O a warp holds
@@ -215,6 +219,14 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
                     mma_bf16(sc[2 * jp + 1], af[cur], bf[cur][jp][2], bf[cur][jp][3]);
                 }
             }
+            if (softcap > 0.f) {
+                // (what follows multiplies by scale * log2 e: the capped score divided by scale)
+                const float in = scale / softcap, back = softcap / scale;
+#pragma unroll
+                for (int j = 0; j < NT_S; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sc[j][e] = back * tanhf(sc[j][e] * in);
+            }
             // mask, online softmax (base-2 domain)
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -321,6 +333,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
             }
             continue;
         }
+        if (sink != nullptr)
+            l[h] += (m[h] == -INFINITY) ? 1.f : exp2f(sink[head] * 1.4426950408889634f - m[h]);
         float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
         if (gate != nullptr) {
             const float z = __bfloat162float(gate[(size_t)(q0 + tl) * ldg + head]);
@@ -349,7 +363,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
 // head), a thread two neighbouring columns; the splits' weights are formed once per block.
 __global__ void __launch_bounds__(128) attention_kv_combine_kernel(
     const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits, bf16* __restrict__ out,
-    int ldo, int H, const bf16* __restrict__ gate, int ldg, float* __restrict__ out_f32) {
+    int ldo, int H, const bf16* __restrict__ gate, int ldg, float* __restrict__ out_f32,
+    const float* __restrict__ sink) {
     __shared__ float wgt[32];
     __shared__ float inv_s;
     pdl_wait();
@@ -363,9 +378,10 @@ __global__ void __launch_bounds__(128) attention_kv_combine_kernel(
         const float ls = s < splits ? part_ml[2 * (base + s) + 1] : 0.f;
         const float M = warp_max(ms);
         const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
-        const float L = warp_sum(ls * w);
+        float L = warp_sum(ls * w);
         wgt[s] = w;
         if (s == 0) {
+            if (sink != nullptr) L += (M == -INFINITY) ? 1.f : exp2f(sink[head] * 1.4426950408889634f - M);
             float inv = L > 0.f ? 1.f / L : 0.f;
             if (gate != nullptr) inv *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[t * ldg + head])));
             inv_s = inv;
@@ -424,7 +440,8 @@ static int launch_attention_kv_mma(const bf16* q, int ldq, const bf16* kc, const
                                    const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
                                    int H, int Hkv, int maps, int ps, int num_pages, float scale, int window,
                                    const bf16* gate, int ldg, int splits, float* part_o, float* part_ml,
-                                   int narrow, int fold, cudaStream_t st) {
+                                   int narrow, int fold, cudaStream_t st, float softcap = 0.f,
+                                   const float* sink = nullptr) {
     // `fold` > 1: H counts (head, map) pairs, `maps` is 1, DK is fold times a map's key size.
     // `narrow`: every tile of the list holds at most 16 rows (a step of single tokens with at most
     // 16 query heads a kv head).
@@ -434,6 +451,7 @@ static int launch_attention_kv_mma(const bf16* q, int ldq, const bf16* kc, const
     if (splits < 1 || splits > 32 || (splits > 1 && (part_o == nullptr || part_ml == nullptr || H / Hkv > BM)))
         return SLB_ERR_BAD_ARG;
     if (narrow && H / Hkv > 16) return SLB_ERR_BAD_ARG;
+    if (softcap < 0.f || (sink != nullptr && (maps != 1 || fold != 1))) return SLB_ERR_BAD_ARG;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || scale <= 0.f ||
         (tied && DV > DK) || ldq % 8 != 0 || ldo % 2 != 0 || maps < 1 || (maps > 1 && tied) || fold < 1 ||
         (fold > 1 && (maps != 1 || tied || DK % (8 * fold) != 0 || H % fold != 0)))
@@ -452,11 +470,11 @@ static int launch_attention_kv_mma(const bf16* q, int ldq, const bf16* kc, const
                              dim3(num_tiles * Hkv * maps, splits), dim3(NTHREADS), smem, st,
                              q, ldq, kc, tied ? kc : vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len,
                              tile_seq, tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window,
-                             gate, ldg, splits, part_o, part_ml, maps, out_f32, q_rows, fold);
+                             gate, ldg, splits, part_o, part_ml, maps, out_f32, q_rows, fold, softcap, scale, sink);
     if (e != 0 || splits == 1) return e;
     // (one tile a token: num_tiles is the number of tokens)
     return slb_launch(attention_kv_combine_kernel, dim3(num_tiles, H * maps), dim3(128), 0, st, (const float*)part_o,
-                      (const float*)part_ml, splits, out, ldo, H * maps, gate, ldg, out_f32);
+                      (const float*)part_ml, splits, out, ldo, H * maps, gate, ldg, out_f32, sink);
 }
 // `tied`: the values are the first DV elements of the key rows (vc is ignored).
 int slb_attention_kv_mma_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int tied, bf16* out,
@@ -468,6 +486,18 @@ int slb_attention_kv_mma_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
     return launch_attention_kv_mma(q, ldq, kc, vc, tied, out, nullptr, ldo, block_table, max_pages, cu_q, ctx_len,
                                    tile_seq, tile_row0, num_tiles, H, Hkv, 1, ps, num_pages, scale, window, gate,
                                    ldg, splits, part_o, part_ml, narrow, 1, st);
+}
+// The same with a soft cap on the scaled scores (`softcap` > 0: s <- softcap tanh(s / softcap)) and a
+// sink a head (`sink` [H] float32 or null) in the softmax's denominator.
+int slb_attention_kv_mma_capped_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int tied, bf16* out,
+                                     int ldo, const int* block_table, int max_pages, const int* cu_q,
+                                     const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
+                                     int H, int Hkv, int ps, int num_pages, float scale, int window,
+                                     const bf16* gate, int ldg, int splits, float* part_o, float* part_ml,
+                                     int narrow, float softcap, const float* sink, cudaStream_t st) {
+    return launch_attention_kv_mma(q, ldq, kc, vc, tied, out, nullptr, ldo, block_table, max_pages, cu_q, ctx_len,
+                                   tile_seq, tile_row0, num_tiles, H, Hkv, 1, ps, num_pages, scale, window, gate,
+                                   ldg, splits, part_o, part_ml, narrow, 1, st, softcap, sink);
 }
 // `maps` attention maps a head; float32 results [token][head][map][DV] with rows `ldo` floats apart
 int slb_attention_kv_mma_maps_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int maps, float* out,

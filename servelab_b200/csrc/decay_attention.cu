@@ -3,6 +3,11 @@
 //     S_t = decay_h S_{t-1} + k_t v_t^T        (S: D x Dv per head, float32, kept in a state slot)
 //     o_t = S_t^T q_t
 //
+// or, with `gate_z`, with a decay of its own for every token and key channel (the rows of S that
+// belong to key channel d are multiplied by alpha_t[d] = sigmoid(z_t[d])^(1 / tau)):
+//
+//     S_t = diag(alpha_t) S_{t-1} + k_t v_t^T
+//
 // q, k and v are columns of one projected row per token.  Before they enter the recurrence the
 // kernel applies, each optional: an activation (SiLU) on q, k and v; a rotation of the first
 // `rot_dims` elements of every query and key head (element i with element i + rot_dims / 2, angle
@@ -47,11 +52,13 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS, R <= 16 ? 4 : 2) decay_atten
     float* ks = qs + DA_TT * LD;                 // [DA_TT][LD]
     float* vs = ks + DA_TT * LD;                 // [DA_TT][DA_EV]
     float* part = vs + DA_TT * DA_EV;            // [DA_TT][DA_PARTS][DA_EV]
+    float* as = part + DA_TT * DA_PARTS * DA_EV; // [DA_TT][LD]: the decays of a token's key channels (gated form)
+    const bool gated = a.gate_z != nullptr;
     const int tid = threadIdx.x, p = tid >> 5, e = tid & 31;
     const int col = e0 + e;
     const bool live = col < Dv;
-    const float dec = a.decay[h];
-    float* srow = a.state + ((size_t)slot * a.H + h) * (size_t)D * Dv;
+    const float dec = gated ? 1.f : a.decay[h];
+    float* srow = a.state + (size_t)slot * (size_t)a.state_stride + (size_t)h * D * Dv;
 
     float st[R];
 #pragma unroll
@@ -66,15 +73,22 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS, R <= 16 ? 4 : 2) decay_atten
             const int j = idx / LD, c = idx - j * LD;
             const int pp = c / Dpad, i = c - pp * Dpad;
             const int d = pp * Dp + i;
-            float qv = 0.f, kv = 0.f;                      // (the padding multiplies state elements that stay 0)
+            float qv = 0.f, kv = 0.f, av = 1.f;            // (the padding multiplies state elements that stay 0)
             if (i < Dp && d < D) {
                 const T* row = proj + (size_t)(q0 + t0 + j) * a.ld;
                 const int pos = a.positions[q0 + t0 + j];
-                qv = da_prepared(row + a.q_off + h * D, d, pos, a);
+                qv = da_prepared(row + a.q_off + h * D, d, pos, a) * a.q_scale;
                 kv = da_prepared(row + a.k_off + h * D, d, pos, a) * a.k_scale;
+                if (gated) {
+                    float z = a.gate_z[(size_t)(q0 + t0 + j) * a.ld_gate + h * D + d];
+                    if (a.gate_bias != nullptr) z += a.gate_bias[h * D + d];
+                    // log sigmoid(z) = min(z, 0) - log(1 + exp(-|z|))
+                    av = expf((fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * a.gate_inv_tau);
+                }
             }
             qs[idx] = qv;
             ks[idx] = kv;
+            if (gated) as[idx] = av;
         }
         for (int idx = tid; idx < n * DA_EV; idx += DA_EV * DA_PARTS) {
             const int j = idx / DA_EV, c = e0 + (idx - j * DA_EV);
@@ -91,6 +105,25 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS, R <= 16 ? 4 : 2) decay_atten
             const float4* qj = reinterpret_cast<const float4*>(qs + j * LD + p * Dpad);
             const float4* kj = reinterpret_cast<const float4*>(ks + j * LD + p * Dpad);
             float acc = 0.f;
+            if (gated) {
+                const float4* aj = reinterpret_cast<const float4*>(as + j * LD + p * Dpad);
+#pragma unroll
+                for (int i4 = 0; i4 < R / 4; ++i4) {
+                    if (i4 * 4 < Dp) {
+                        const float4 k4 = kj[i4], q4 = qj[i4], a4 = aj[i4];
+                        st[4 * i4] = fmaf(a4.x, st[4 * i4], k4.x * v);
+                        acc = fmaf(st[4 * i4], q4.x, acc);
+                        st[4 * i4 + 1] = fmaf(a4.y, st[4 * i4 + 1], k4.y * v);
+                        acc = fmaf(st[4 * i4 + 1], q4.y, acc);
+                        st[4 * i4 + 2] = fmaf(a4.z, st[4 * i4 + 2], k4.z * v);
+                        acc = fmaf(st[4 * i4 + 2], q4.z, acc);
+                        st[4 * i4 + 3] = fmaf(a4.w, st[4 * i4 + 3], k4.w * v);
+                        acc = fmaf(st[4 * i4 + 3], q4.w, acc);
+                    }
+                }
+                part[(j * DA_PARTS + p) * DA_EV + e] = acc;
+                continue;
+            }
 #pragma unroll
             for (int i4 = 0; i4 < R / 4; ++i4) {
                 if (i4 * 4 < Dp) {                         // (the same for every thread)
@@ -128,8 +161,14 @@ __global__ void __launch_bounds__(DA_EV * DA_PARTS, R <= 16 ? 4 : 2) decay_atten
 }
 
 template <typename T>
-static int launch_decay_attention(const DecayAttnArgs* a, int num_seqs, cudaStream_t st) {
+static int launch_decay_attention(const DecayAttnArgs* a_in, int num_seqs, cudaStream_t st) {
     if (num_seqs <= 0) return 0;
+    DecayAttnArgs args = *a_in;
+    if (args.state_stride <= 0) args.state_stride = (long long)args.H * args.D * args.Dv;
+    const DecayAttnArgs* a = &args;
+    if (a->state_stride < (long long)a->H * a->D * a->Dv) return SLB_ERR_BAD_ARG;
+    if ((a->gate_z == nullptr) == (a->decay == nullptr)) return SLB_ERR_BAD_ARG;      // one of the two
+    if (a->gate_z != nullptr && (a->ld_gate < a->H * a->D || !(a->gate_inv_tau > 0.f))) return SLB_ERR_BAD_ARG;
     if (a->H <= 0 || a->D <= 0 || a->Dv <= 0 || a->num_slots <= 0 || (a->rot_dims & 1) || a->rot_dims < 0 ||
         a->rot_dims > a->D || (a->rot_dims > 0 && a->freq == nullptr) || a->act < 0 || a->act > 1)
         return SLB_ERR_BAD_ARG;
@@ -137,7 +176,8 @@ static int launch_decay_attention(const DecayAttnArgs* a, int num_seqs, cudaStre
     const int vz = (a->Dv + DA_EV - 1) / DA_EV;
     if (vz > 65535) return SLB_ERR_TOO_LARGE;
     const int dpad = ((a->D + DA_PARTS - 1) / DA_PARTS + 3) / 4 * 4;
-    const size_t smem = ((size_t)2 * DA_TT * DA_PARTS * dpad + DA_TT * DA_EV + DA_TT * DA_PARTS * DA_EV) * sizeof(float);
+    const size_t smem = ((size_t)(a->gate_z != nullptr ? 3 : 2) * DA_TT * DA_PARTS * dpad + DA_TT * DA_EV +
+                         DA_TT * DA_PARTS * DA_EV) * sizeof(float);
     if (a->D <= 16 * DA_PARTS)
         return slb_launch(decay_attention_kernel<T, 16>, dim3(num_seqs, a->H, vz), dim3(DA_EV * DA_PARTS), smem, st, *a);
     return slb_launch(decay_attention_kernel<T, DA_MAX_D / DA_PARTS>, dim3(num_seqs, a->H, vz), dim3(DA_EV * DA_PARTS),

@@ -15,6 +15,13 @@ struct DecayAttnArgs {
     const int* positions; const int* cu_q; const int* state_slots;
     float* state; int num_slots;   // [num_slots][H][D][Dv]
     float* out; int ldo;           // [T][H * Dv] float32
+    // appended: a decay of its own for every token and key channel instead of `decay` (which is
+    // then null), alpha = sigmoid(z)^(1 / tau) with z = gate_z[token][h * D + d] + gate_bias[h * D + d]
+    // (float32), formed in float32 as exp(log sigmoid(z) / tau); a factor on the queries; and the
+    // distance in floats between the records of two slots (0: H * D * Dv)
+    const float* gate_z; int ld_gate; const float* gate_bias; float gate_inv_tau;
+    float q_scale;
+    long long state_stride;
 };
 
 __device__ __forceinline__ float da_silu(float z) { return z / (1.0f + expf(-z)); }

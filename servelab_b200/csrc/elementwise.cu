@@ -334,17 +334,23 @@ __device__ __forceinline__ float silu_mul_fast(float g, float u) {
 __device__ __forceinline__ float gelu_tanh_mul(float g, float u) {
     return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
 }
-template <int ACT> __device__ __forceinline__ float act_mul(float g, float u) {
-    return ACT == 1 ? gelu_tanh_mul(g, u) : silu_mul(g, u);
+// the clamped form: g = min(gate, limit), u = clamp(up, -limit, limit), g sigmoid(alpha g) (u + 1)
+__device__ __forceinline__ float swish_clamped_mul(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
 }
-template <int ACT> __device__ __forceinline__ float act_mul_fast(float g, float u) {
-    return ACT == 1 ? gelu_tanh_mul(g, u) : silu_mul_fast(g, u);
+template <int ACT> __device__ __forceinline__ float act_mul(float g, float u, float p0, float p1) {
+    return ACT == 2 ? swish_clamped_mul(g, u, p0, p1) : ACT == 1 ? gelu_tanh_mul(g, u) : silu_mul(g, u);
+}
+template <int ACT> __device__ __forceinline__ float act_mul_fast(float g, float u, float p0, float p1) {
+    return ACT == 2 ? swish_clamped_mul(g, u, p0, p1) : ACT == 1 ? gelu_tanh_mul(g, u) : silu_mul_fast(g, u);
 }
 
-// ACT 0: SiLU; 1: GELU (tanh form)
+// ACT 0: SiLU; 1: GELU (tanh form); 2: the clamped form with p0 = limit, p1 = alpha
 template <typename T, int V, int ACT>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
-                              int ld_gu, int ld_out, int block) {
+                              int ld_gu, int ld_out, int block, float p0, float p1) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.y;
@@ -365,15 +371,15 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-            r2[e] = __floats2bfloat162_rn(act_mul_fast<ACT>(g.x, u.x), act_mul_fast<ACT>(g.y, u.y));
+            r2[e] = __floats2bfloat162_rn(act_mul_fast<ACT>(g.x, u.x, p0, p1), act_mul_fast<ACT>(g.y, u.y, p0, p1));
         }
         *reinterpret_cast<uint4*>(o + i) = res;
     } else if constexpr (V == 4) {
         const float4 g = load4(row + gi), u = load4(row + ui);
-        store4(o + i, make_float4(act_mul<ACT>(g.x, u.x), act_mul<ACT>(g.y, u.y), act_mul<ACT>(g.z, u.z),
-                                  act_mul<ACT>(g.w, u.w)));
+        store4(o + i, make_float4(act_mul<ACT>(g.x, u.x, p0, p1), act_mul<ACT>(g.y, u.y, p0, p1),
+                                  act_mul<ACT>(g.z, u.z, p0, p1), act_mul<ACT>(g.w, u.w, p0, p1)));
     } else {
-        o[i] = from_float<T>(act_mul<ACT>(to_float(row[gi]), to_float(row[ui])));
+        o[i] = from_float<T>(act_mul<ACT>(to_float(row[gi]), to_float(row[ui]), p0, p1));
     }
 }
 
@@ -415,20 +421,20 @@ static int launch_add_rmsnorm(float* resid, const TD* delta, const float* parts,
 
 template <typename T, int ACT>
 static int launch_swiglu(const T* gu, T* out, int T_, int inter, int ld_gu, int ld_out, int block,
-                         cudaStream_t st) {
+                         cudaStream_t st, float p0 = 0.f, float p1 = 0.f) {
     if (T_ <= 0) return 0;
     if (inter <= 0 || T_ > 65535 || block < 0 || (block > 0 && inter % block)) return SLB_ERR_BAD_ARG;
     if constexpr (sizeof(T) == 2) {
         if (inter % 8 == 0 && block % 8 == 0 && ld_gu % 8 == 0 && ld_out % 8 == 0 &&
             ((uintptr_t)gu | (uintptr_t)out) % 16 == 0)
             return slb_launch(swiglu_kernel<T, 8, ACT>, dim3((inter / 8 + 255) / 256, T_), dim3(256), 0, st,
-                              gu, out, inter, ld_gu, ld_out, block);
+                              gu, out, inter, ld_gu, ld_out, block, p0, p1);
     }
     if (inter % 4 == 0 && block % 4 == 0 && ld_gu % 4 == 0 && ld_out % 4 == 0)
         return slb_launch(swiglu_kernel<T, 4, ACT>, dim3((inter / 4 + 255) / 256, T_), dim3(256), 0, st,
-                          gu, out, inter, ld_gu, ld_out, block);
+                          gu, out, inter, ld_gu, ld_out, block, p0, p1);
     return slb_launch(swiglu_kernel<T, 1, ACT>, dim3((inter + 255) / 256, T_), dim3(256), 0, st, gu,
-                      out, inter, ld_gu, ld_out, block);
+                      out, inter, ld_gu, ld_out, block, p0, p1);
 }
 
 SLB_DEFINE_PDL_SWITCH
@@ -515,6 +521,17 @@ int slb_gated_act_bf16(const bf16* gu, bf16* out, int T, int inter, int ld_gu, i
     if (act == 0) return launch_swiglu<bf16, 0>(gu, out, T, inter, ld_gu, ld_out, block, st);
     if (act == 1) return launch_swiglu<bf16, 1>(gu, out, T, inter, ld_gu, ld_out, block, st);
     return SLB_ERR_BAD_ARG;
+}
+// the clamped form: g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(alpha g) (u + 1)
+int slb_gated_act_clamped_f32(const float* gu, float* out, int T, int inter, int ld_gu, int ld_out, int block,
+                              float limit, float alpha, cudaStream_t st) {
+    if (!(limit > 0.f)) return SLB_ERR_BAD_ARG;
+    return launch_swiglu<float, 2>(gu, out, T, inter, ld_gu, ld_out, block, st, limit, alpha);
+}
+int slb_gated_act_clamped_bf16(const bf16* gu, bf16* out, int T, int inter, int ld_gu, int ld_out, int block,
+                               float limit, float alpha, cudaStream_t st) {
+    if (!(limit > 0.f)) return SLB_ERR_BAD_ARG;
+    return launch_swiglu<bf16, 2>(gu, out, T, inter, ld_gu, ld_out, block, st, limit, alpha);
 }
 
 }  // extern "C"

@@ -5,8 +5,11 @@
 //     * RMS norm over its first `norm_dims` elements with a weight shared by the heads
 //       (x / sqrt(mean(x^2) + eps) * w; 0: no norm);
 //     * rotation of `rot_dims` elements starting at `rot_off`: element 2i is paired with element
-//       2i + 1, the pair (u, v) at position p becomes (u c - v s, v c + u s) with
+//       2i + 1 (or, with `rot_half`, element i with element i + rot_dims / 2), the pair (u, v) at
+//       position p becomes (u c - v s, v c + u s) with
 //       c = mag cos(p f_i), s = mag sin(p f_i) (a table of frequencies, one factor on both);
+//     * after the rotation, division of the first `unit_dims` elements by their root mean square
+//       (no weight; 0: none);
 //     * queries go to the q buffer -- head h at h * q_head_stride, without its first `q_skip`
 //       elements (a latent attention replaces them by their product with a matrix and keeps the
 //       rotated rest) --, keys into the request's page (block-table look-up here);
@@ -38,6 +41,7 @@ struct HeadPrepArgs {
     int max_pages, page_size, num_pages;
     void* q_out; int ldq; void* k_cache; void* v_cache;
     int q_head_stride, q_skip;
+    int rot_half, q_unit_dims, k_unit_dims;
 };
 
 template <typename T>
@@ -76,18 +80,18 @@ __global__ void __launch_bounds__(HP_WARPS * 32) head_prep_kernel(const HeadPrep
     for (int u = blockIdx.y * HP_WARPS + warp; u < units; u += gridDim.y * HP_WARPS) {
         const T* src;
         T* dst = nullptr;
-        int D, norm_dims = 0, rot_off = 0;
+        int D, norm_dims = 0, rot_off = 0, unit_dims = 0;
         const float* nw = nullptr;
         bool rotate = a.rot_dims > 0;
         int vhead = -1, skip = 0;
         if (u < a.H) {
-            D = a.Dq; norm_dims = a.q_norm_dims; nw = a.q_norm_w; rot_off = a.q_rot_off;
+            D = a.Dq; norm_dims = a.q_norm_dims; nw = a.q_norm_w; rot_off = a.q_rot_off; unit_dims = a.q_unit_dims;
             src = row + a.q_off + (size_t)u * D;
             dst = reinterpret_cast<T*>(a.q_out) + (size_t)t * a.ldq + (size_t)u * a.q_head_stride;
             skip = a.q_skip;
         } else if (u < a.H + a.G) {
             const int g = u - a.H;
-            D = a.Dk; norm_dims = a.k_norm_dims; nw = a.k_norm_w; rot_off = a.k_rot_off;
+            D = a.Dk; norm_dims = a.k_norm_dims; nw = a.k_norm_w; rot_off = a.k_rot_off; unit_dims = a.k_unit_dims;
             src = row + a.k_off + (size_t)g * D;
             if (a.k_cache != nullptr && slot >= 0)
                 dst = reinterpret_cast<T*>(a.k_cache) + (size_t)(slot + (long long)g * a.page_size) * D;
@@ -117,15 +121,27 @@ __global__ void __launch_bounds__(HP_WARPS * 32) head_prep_kernel(const HeadPrep
                 for (int i = lane; i < norm_dims; i += 32) ss += buf[i] * buf[i];
                 ss = warp_sum(ss);
                 const float r = 1.0f / sqrtf(ss / (float)norm_dims + a.eps);
-                for (int i = lane; i < norm_dims; i += 32) buf[i] = buf[i] * r * nw[i];
+                for (int i = lane; i < norm_dims; i += 32) buf[i] = buf[i] * r * (nw != nullptr ? nw[i] : 1.f);
             }
             if (rotate) {
-                for (int i = lane; i < a.rot_dims / 2; i += 32) {
+                __syncwarp();                          // (the norm wrote elements other lanes rotate)
+                const int half = a.rot_dims / 2;
+                for (int i = lane; i < half; i += 32) {
                     const float sn = sn_tab[i], cs = cs_tab[i];
-                    const float x = buf[rot_off + 2 * i], y = buf[rot_off + 2 * i + 1];
-                    buf[rot_off + 2 * i] = x * cs - y * sn;
-                    buf[rot_off + 2 * i + 1] = y * cs + x * sn;
+                    const int ix = a.rot_half ? rot_off + i : rot_off + 2 * i;
+                    const int iy = a.rot_half ? rot_off + i + half : rot_off + 2 * i + 1;
+                    const float x = buf[ix], y = buf[iy];
+                    buf[ix] = x * cs - y * sn;
+                    buf[iy] = y * cs + x * sn;
                 }
+            }
+            if (unit_dims > 0) {
+                __syncwarp();
+                float ss = 0.f;
+                for (int i = lane; i < unit_dims; i += 32) ss += buf[i] * buf[i];
+                ss = warp_sum(ss);
+                const float r = 1.0f / sqrtf(ss / (float)unit_dims + a.eps);
+                for (int i = lane; i < unit_dims; i += 32) buf[i] *= r;
             }
         }
         __syncwarp();
@@ -155,10 +171,11 @@ static int launch_head_prep(const HeadPrepArgs& a, int num_tokens, cudaStream_t 
     const int maxd = a.Dq > a.Dk ? (a.Dq > a.Dv ? a.Dq : a.Dv) : (a.Dk > a.Dv ? a.Dk : a.Dv);
     if (a.H < 0 || a.G < 0 || a.Dq < 0 || a.Dk < 0 || maxd <= 0 || (a.rot_dims & 1)) return SLB_ERR_BAD_ARG;
     if (maxd > HP_MAX_D) return SLB_ERR_TOO_LARGE;
-    if (a.rot_dims > 0 && (a.freq == nullptr || a.q_rot_off + a.rot_dims > a.Dq ||
-                           a.k_rot_off + a.rot_dims > a.Dk))
+    if (a.rot_dims > 0 && (a.freq == nullptr || (a.H > 0 && a.q_rot_off + a.rot_dims > a.Dq) ||
+                           (a.G > 0 && a.k_rot_off + a.rot_dims > a.Dk)))
         return SLB_ERR_BAD_ARG;
     if (a.q_norm_dims > a.Dq || a.k_norm_dims > a.Dk || a.q_skip < 0 || a.q_skip > a.Dq) return SLB_ERR_BAD_ARG;
+    if (a.q_unit_dims < 0 || a.q_unit_dims > a.Dq || a.k_unit_dims < 0 || a.k_unit_dims > a.Dk) return SLB_ERR_BAD_ARG;
     if ((a.k_cache != nullptr || a.v_cache != nullptr) && (a.block_table == nullptr || a.page_size <= 0))
         return SLB_ERR_BAD_ARG;
     const size_t smem = ((size_t)HP_WARPS * maxd + a.rot_dims) * sizeof(float);

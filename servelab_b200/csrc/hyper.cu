@@ -176,7 +176,81 @@ static int launch_group_norm_gate(const float* in, int ldi, int maps, const floa
                       lam, w, eps, factor, gate, ldg, gate_act, out, ldo, T_, groups, size);
 }
 
+// out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w over the first n columns of every row (a latent
+// inside a wider projection); a block a row, float32 arithmetic.
+template <typename T>
+__global__ void __launch_bounds__(256) rms_norm_rows_kernel(const T* __restrict__ x, int ldx,
+                                                            const float* __restrict__ w, float eps,
+                                                            T* __restrict__ out, int ldo, int n) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const T* row = x + (size_t)blockIdx.x * ldx;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const float v = to_float(row[c]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int c = threadIdx.x; c < n; c += blockDim.x)
+        out[(size_t)blockIdx.x * ldo + c] = from_float<T>(to_float(row[c]) * rstd * (w != nullptr ? w[c] : 1.f));
+}
+
+// out[t] = factor * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb): the results of two branches
+// that read the same input, each RMS-normed over the row with a weight of its own, summed.
+// a and b float32 [T, n]; a block a row; float32 arithmetic.
+template <typename T>
+__global__ void __launch_bounds__(256) norm_sum2_kernel(const float* __restrict__ a, int lda,
+                                                        const float* __restrict__ b, int ldb,
+                                                        const float* __restrict__ wa, const float* __restrict__ wb,
+                                                        float eps, float factor, T* __restrict__ out, int ldo, int n) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const float* ra = a + (size_t)blockIdx.x * lda;
+    const float* rb = b + (size_t)blockIdx.x * ldb;
+    float sa = 0.f, sb = 0.f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        sa += ra[c] * ra[c];
+        sb += rb[c] * rb[c];
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float fa = 1.0f / sqrtf(sa / (float)n + eps), fb = 1.0f / sqrtf(sb / (float)n + eps);
+    for (int c = threadIdx.x; c < n; c += blockDim.x)
+        out[(size_t)blockIdx.x * ldo + c] = from_float<T>(factor * (ra[c] * fa * wa[c] + rb[c] * fb * wb[c]));
+}
+
 extern "C" {
+int slb_rms_norm_rows_f32(const float* x, int ldx, const float* w, float eps, float* out, int ldo, int T, int n,
+                          cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (n <= 0 || ldx < n || ldo < n) return SLB_ERR_BAD_ARG;
+    return slb_launch(rms_norm_rows_kernel<float>, dim3(T), dim3(n >= 1024 ? 256 : 128), 0, st, x, ldx, w, eps, out,
+                      ldo, n);
+}
+int slb_rms_norm_rows_bf16(const bf16* x, int ldx, const float* w, float eps, bf16* out, int ldo, int T, int n,
+                           cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (n <= 0 || ldx < n || ldo < n) return SLB_ERR_BAD_ARG;
+    return slb_launch(rms_norm_rows_kernel<bf16>, dim3(T), dim3(n >= 1024 ? 256 : 128), 0, st, x, ldx, w, eps, out,
+                      ldo, n);
+}
+int slb_norm_sum2_f32(const float* a, int lda, const float* b, int ldb, const float* wa, const float* wb, float eps,
+                      float factor, float* out, int ldo, int T, int n, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (n <= 0 || lda < n || ldb < n || ldo < n || wa == nullptr || wb == nullptr) return SLB_ERR_BAD_ARG;
+    return slb_launch(norm_sum2_kernel<float>, dim3(T), dim3(256), 0, st, a, lda, b, ldb, wa, wb, eps, factor, out,
+                      ldo, n);
+}
+int slb_norm_sum2_bf16(const float* a, int lda, const float* b, int ldb, const float* wa, const float* wb, float eps,
+                       float factor, bf16* out, int ldo, int T, int n, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (n <= 0 || lda < n || ldb < n || ldo < n || wa == nullptr || wb == nullptr) return SLB_ERR_BAD_ARG;
+    return slb_launch(norm_sum2_kernel<bf16>, dim3(T), dim3(256), 0, st, a, lda, b, ldb, wa, wb, eps, factor, out,
+                      ldo, n);
+}
 int slb_hyper_max_streams() { return HY_MAX_STREAMS; }
 int slb_embed_norm_streams_f32(const int* ids, const float* table, const float* w, float eps, float* out, int T,
                                int n, int h, int vocab, cudaStream_t st) {

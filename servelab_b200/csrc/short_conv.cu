@@ -18,6 +18,11 @@
 // single tokens the thread that computes (request, channel) is the only one that reads that
 // column of the record, so it shifts it on the spot (`update_inline`).  With portions other
 // blocks may still read the old record, so a second, small kernel writes it afterwards.
+//
+// With no key heads (Hkv = 0) every channel is a "query" channel: the kernel is then a plain
+// convolution of the first q_size columns into q_out, which a mixer runs on q | k | v before its
+// head kernel.  The records of two requests lie `state_stride` floats apart (a record may be part of
+// a larger one).
 #include "common.cuh"
 
 #define SC_MAX_TAPS 64
@@ -73,7 +78,7 @@ __global__ void __launch_bounds__(256) qk_conv_cache_kernel(
     const int* __restrict__ seq_of_token, const int* __restrict__ positions,
     const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
     float temp_coef, int temp_every, T* __restrict__ q_out, int ldq, T* __restrict__ k_cache,
-    int q_size, int Hkv, int D, int update_inline) {
+    int q_size, int Hkv, int D, int update_inline, long long state_stride) {
     const int C = q_size + Hkv * D;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     pdl_launch_dependents();
@@ -85,7 +90,7 @@ __global__ void __launch_bounds__(256) qk_conv_cache_kernel(
     const int j = t - q0;
     const int pos = positions[t];
     const int hist = taps - 1;
-    float* st = state != nullptr ? state + (size_t)state_slots[s] * hist * C + c : nullptr;
+    float* st = state != nullptr ? state + (size_t)state_slots[s] * state_stride + c : nullptr;
     float y[VEC];
 #pragma unroll
     for (int v = 0; v < VEC; ++v) y[v] = 0.f;
@@ -128,7 +133,7 @@ __global__ void __launch_bounds__(256) qk_conv_cache_kernel(
 template <typename T>
 __global__ void __launch_bounds__(256) conv_state_update_kernel(
     const T* __restrict__ proj, int ldp, int taps, float* __restrict__ state,
-    const int* __restrict__ state_slots, const int* __restrict__ cu_q, int C) {
+    const int* __restrict__ state_slots, const int* __restrict__ cu_q, int C, long long state_stride) {
     pdl_launch_dependents();
     pdl_wait();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -137,7 +142,7 @@ __global__ void __launch_bounds__(256) conv_state_update_kernel(
     const int q0 = cu_q[s], n = cu_q[s + 1] - q0;
     if (n <= 0) return;
     const int hist = taps - 1;
-    float* st = state + (size_t)state_slots[s] * hist * C + c;
+    float* st = state + (size_t)state_slots[s] * state_stride + c;
     // ascending i: row i + n of the old record is read before any row >= i + 1 is written
     for (int i = 0; i < hist; ++i) {
         const int src = i + n - hist;              // index into the portion, or before it
@@ -150,9 +155,14 @@ static int launch_conv(const T* proj, int ldp, const float* taps_w, int taps, fl
                        const int* state_slots, const int* cu_q, const int* seq_of_token,
                        const int* positions, const int* block_table, int max_pages, int page_size,
                        int num_pages, float temp_coef, int temp_every, T* q_out, int ldq, T* k_cache,
-                       int T_tokens, int S, int q_size, int Hkv, int D, int decode_only, cudaStream_t st) {
+                       int T_tokens, int S, int q_size, int Hkv, int D, int decode_only, long long state_stride,
+                       cudaStream_t st) {
     if (T_tokens <= 0) return 0;
-    if (taps < 1 || q_size < 0 || Hkv <= 0 || D <= 0 || page_size <= 0 || temp_every <= 0 ||
+    if (state_stride <= 0) state_stride = (long long)(taps - 1) * (q_size + Hkv * D);
+    if (state_stride < (long long)(taps - 1) * (q_size + Hkv * D)) return SLB_ERR_BAD_ARG;
+    if (Hkv == 0) { D = 0; page_size = 1; }             // (no key channels: a convolution alone)
+    if (taps < 1 || q_size < 0 || Hkv < 0 || (Hkv > 0 && D <= 0) || q_size + Hkv * D <= 0 || page_size <= 0 ||
+        temp_every <= 0 ||
         (taps > 1 && state == nullptr) || T_tokens > 65535 || S > 65535)
         return SLB_ERR_BAD_ARG;
     if (taps > SC_MAX_TAPS) return SLB_ERR_TOO_LARGE;
@@ -160,6 +170,7 @@ static int launch_conv(const T* proj, int ldp, const float* taps_w, int taps, fl
     const int inline_update = decode_only && taps > 1 ? 1 : 0;
     constexpr int V = 16 / (int)sizeof(T);             // channels of one 16-byte access
     const bool vec = q_size % V == 0 && D % V == 0 && ldp % V == 0 && ldq % V == 0 && C % 4 == 0 &&
+                     state_stride % 4 == 0 &&
                      (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)state |
                        (uintptr_t)taps_w) & 15) == 0;
     int rc;
@@ -168,16 +179,16 @@ static int launch_conv(const T* proj, int ldp, const float* taps_w, int taps, fl
         rc = slb_launch(qk_conv_cache_kernel<T, V>, dim3((C / V + threads - 1) / threads, T_tokens), dim3(threads),
                         0, st, proj, ldp, taps_w, taps, state, state_slots, cu_q, seq_of_token, positions,
                         block_table, max_pages, page_size, num_pages, temp_coef, temp_every, q_out, ldq,
-                        k_cache, q_size, Hkv, D, inline_update);
+                        k_cache, q_size, Hkv, D, inline_update, state_stride);
     } else {
         rc = slb_launch(qk_conv_cache_kernel<T, 1>, dim3((C + 255) / 256, T_tokens), dim3(256), 0, st, proj,
                         ldp, taps_w, taps, state, state_slots, cu_q, seq_of_token, positions, block_table,
                         max_pages, page_size, num_pages, temp_coef, temp_every, q_out, ldq, k_cache, q_size,
-                        Hkv, D, inline_update);
+                        Hkv, D, inline_update, state_stride);
     }
     if (rc != 0 || taps == 1 || inline_update) return rc;
     return slb_launch(conv_state_update_kernel<T>, dim3((C + 255) / 256, S), dim3(256), 0, st, proj, ldp,
-                      taps, state, state_slots, cu_q, C);
+                      taps, state, state_slots, cu_q, C, state_stride);
 }
 
 extern "C" {
@@ -186,19 +197,19 @@ int slb_qk_conv_cache_f32(const float* proj, int ldp, const float* taps_w, int t
                           const int* positions, const int* block_table, int max_pages, int page_size,
                           int num_pages, float temp_coef, int temp_every, float* q_out, int ldq,
                           float* k_cache, int T_tokens, int S, int q_size, int Hkv, int D,
-                          int decode_only, cudaStream_t st) {
+                          int decode_only, long long state_stride, cudaStream_t st) {
     return launch_conv<float>(proj, ldp, taps_w, taps, state, state_slots, cu_q, seq_of_token, positions,
                               block_table, max_pages, page_size, num_pages, temp_coef, temp_every, q_out,
-                              ldq, k_cache, T_tokens, S, q_size, Hkv, D, decode_only, st);
+                              ldq, k_cache, T_tokens, S, q_size, Hkv, D, decode_only, state_stride, st);
 }
 int slb_qk_conv_cache_bf16(const bf16* proj, int ldp, const float* taps_w, int taps, float* state,
                            const int* state_slots, const int* cu_q, const int* seq_of_token,
                            const int* positions, const int* block_table, int max_pages, int page_size,
                            int num_pages, float temp_coef, int temp_every, bf16* q_out, int ldq,
                            bf16* k_cache, int T_tokens, int S, int q_size, int Hkv, int D,
-                           int decode_only, cudaStream_t st) {
+                           int decode_only, long long state_stride, cudaStream_t st) {
     return launch_conv<bf16>(proj, ldp, taps_w, taps, state, state_slots, cu_q, seq_of_token, positions,
                              block_table, max_pages, page_size, num_pages, temp_coef, temp_every, q_out,
-                             ldq, k_cache, T_tokens, S, q_size, Hkv, D, decode_only, st);
+                             ldq, k_cache, T_tokens, S, q_size, Hkv, D, decode_only, state_stride, st);
 }
 }

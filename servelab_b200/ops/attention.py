@@ -125,13 +125,17 @@ def prepare_kv_attention(key_dim: int, value_dim: int, dtype: torch.dtype) -> No
 
 
 def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk, Dv, page_size, scale,
-                 window, head_gate) -> None:
+                 window, head_gate, softcap=None, sink=None) -> None:
     """Attention with keys of ``Dk`` and values of ``Dv`` elements (value rows ``v_row_stride``
     apart in ``v_cache``, which may be the key cache: the values are then a prefix of the key
     rows), causal with an optional window, head h's row times sigmoid(head_gate[t, h]) if given.
+    ``softcap``: a scaled score s becomes softcap tanh(s / softcap); ``sink`` float32 [H]: a
+    number a head whose exponential joins the softmax's denominator.  The mma.sync and the plain
+    kernel take both; the tcgen05 kernels take neither, so a mixer that has one does not reach them.
     float32, or sizes the tensor-core kernel does not take: the plain kernel."""
     tied = v_cache.data_ptr() == k_cache.data_ptr() and v_row_stride == Dk
-    if (Dk == Dv and not tied and v_row_stride == Dv and q.dtype == torch.bfloat16 and not force_generic
+    modified = bool(softcap) or sink is not None
+    if (Dk == Dv and not tied and not modified and v_row_stride == Dv and q.dtype == torch.bfloat16 and not force_generic
             and use_equal_size_kernels and K.has_fast_attention(Dk) and Dk in (64, 128)):
         # keys and values of one size the tcgen05 kernels take: the framework's attention for
         # equal sizes (tcgen05 prefill, one-launch decode), then the gate in a pass of its own
@@ -141,16 +145,16 @@ def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk,
         return
     if _kv_fast(Dk, Dv, q.dtype) and (tied or v_row_stride == Dv) and q.stride(0) % 8 == 0 \
             and out.stride(0) % 2 == 0:
-        if (not ctx.decode_only and out.stride(0) % 8 == 0
+        if (not ctx.decode_only and not modified and out.stride(0) % 8 == 0
                 and K.attention_kv_tc_takes(Dk, Dv, page_size, H // Hkv, tied)):
             K.attention_kv_tc(ctx, q, k_cache, v_cache, tied, out, table, H, Hkv, Dk, Dv, page_size, scale,
                               window, head_gate)
             return
         K.attention_kv_mma(ctx, q, k_cache, v_cache, tied, out, table, H, Hkv, Dk, Dv, page_size, scale,
-                           window, head_gate)
+                           window, head_gate, softcap or 0.0, sink)
         return
     K.attention_kv(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk, Dv, page_size, scale,
-                   window, head_gate)
+                   window, head_gate, softcap or 0.0, sink)
 
 
 # ------------------------------------------------- several attention maps a head

@@ -344,7 +344,27 @@ def qk_conv_cache(proj: torch.Tensor, taps_w: torch.Tensor, state: Optional[torc
                ctx.positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
                _num_pages(k_cache), float(temp_coef), int(temp_every), q_out.data_ptr(), q_out.stride(0),
                _p(k_cache), proj.shape[0], ctx.num_seqs, q_out.shape[1], num_kv_heads, head_dim,
-               1 if ctx.decode_only else 0, _stream()), "qk_conv_cache")
+               1 if ctx.decode_only else 0, state.stride(0) if state is not None else 0, _stream()),
+            "qk_conv_cache")
+    global launch_count
+    launch_count += n - 1
+
+
+def short_conv(proj: torch.Tensor, taps_w: torch.Tensor, state: Optional[torch.Tensor], ctx,
+               out: torch.Tensor) -> None:
+    """The convolution alone: y_t = sum_i taps_w[i] u_(t - taps + 1 + i) on the first C = out.shape[1]
+    columns of ``proj`` into ``out`` [T, C]; the rows before a portion come from ``state`` (float32
+    [slots, >= (taps - 1) * C], a request's record at ``ctx.state_slots``; rows of the record may be
+    ``state.stride(0)`` apart, so it can be a slice of a larger record), which is left holding the
+    last taps - 1 projected rows."""
+    fn = getattr(L.core(), "slb_qk_conv_cache_" + _suffix(proj.dtype))
+    n = 1 if (taps_w.shape[0] == 1 or ctx.decode_only) else 2
+    L.check(fn(proj.data_ptr(), proj.stride(0), taps_w.data_ptr(), taps_w.shape[0], _p(state),
+               ctx.state_slots.data_ptr(), ctx.cu_q.data_ptr(), ctx.seq_of_token.data_ptr(),
+               ctx.positions.data_ptr(), None, 0, 1, 0, 0.0, 1, out.data_ptr(), out.stride(0),
+               None, proj.shape[0], ctx.num_seqs, out.shape[1], 0, 0,
+               1 if ctx.decode_only else 0, state.stride(0) if state is not None else 0, _stream()),
+            "short_conv")
     global launch_count
     launch_count += n - 1
 
@@ -844,6 +864,7 @@ class _HeadPrepArgs(_ct.Structure):
         ("max_pages", _ct.c_int), ("page_size", _ct.c_int), ("num_pages", _ct.c_int),
         ("q_out", _ct.c_void_p), ("ldq", _ct.c_int), ("k_cache", _ct.c_void_p), ("v_cache", _ct.c_void_p),
         ("q_head_stride", _ct.c_int), ("q_skip", _ct.c_int),
+        ("rot_half", _ct.c_int), ("q_unit_dims", _ct.c_int), ("k_unit_dims", _ct.c_int),
     ]
 
 
@@ -852,11 +873,14 @@ def head_prep(proj: torch.Tensor, ctx, block_table: torch.Tensor, page_size: int
               k_off: int, num_kv_heads: int, k_dim: int, k_norm_w, k_norm_dims: int, k_rot_off: int,
               v_off: int, v_dim: int, freq, rot_dims: int, rot_mag: float, eps: float,
               q_out: torch.Tensor, k_cache, v_cache, lam=None, v_first=None, v_keep=None,
-              q_head_stride: Optional[int] = None, q_skip: int = 0) -> None:
+              q_head_stride: Optional[int] = None, q_skip: int = 0, rot_half: bool = False,
+              q_unit_dims: int = 0, k_unit_dims: int = 0) -> None:
     """One launch between a mixer's first product and its attention: RMS norm of the first
     ``*_norm_dims`` elements of every query / key head (weight shared by the heads; 0: none),
-    rotation of ``rot_dims`` elements from ``*_rot_off`` on (neighbouring pairs; ``freq`` float32
-    [rot_dims / 2]; cos and sin times ``rot_mag``), queries into ``q_out``, keys into the pages;
+    rotation of ``rot_dims`` elements from ``*_rot_off`` on (neighbouring pairs, or with
+    ``rot_half`` element i with element i + rot_dims / 2; ``freq`` float32
+    [rot_dims / 2]; cos and sin times ``rot_mag``), then the first ``*_unit_dims`` elements divided
+    by their root mean square (0: not), queries into ``q_out``, keys into the pages;
     (head h at ``q_out[t, h * q_head_stride:]``, without its first ``q_skip`` elements);
     values (``v_off`` < 0: none) mixed with ``v_first`` by ``lam`` (a float32 scalar on the
     device) or copied to ``v_keep``, and into the pages.  A cache that is None is not written."""
@@ -879,6 +903,7 @@ def head_prep(proj: torch.Tensor, ctx, block_table: torch.Tensor, page_size: int
     a.q_out, a.ldq = q_out.data_ptr(), q_out.stride(0)
     a.k_cache, a.v_cache = _p(k_cache), _p(v_cache)
     a.q_head_stride, a.q_skip = (q_dim if q_head_stride is None else q_head_stride), q_skip
+    a.rot_half, a.q_unit_dims, a.k_unit_dims = int(bool(rot_half)), int(q_unit_dims), int(k_unit_dims)
     fn = getattr(L.core(), "slb_head_prep_" + _suffix(proj.dtype))
     L.check(fn(_ct.byref(a), proj.shape[0], _stream()), "head_prep")
 
@@ -906,10 +931,13 @@ def attention_kv_status(reset: bool = False) -> int:
 
 def attention_kv(ctx, q, k_cache, v_cache, v_row_stride: int, out, block_table, num_heads: int,
                  num_kv_heads: int, k_dim: int, v_dim: int, page_size: int, scale: float, window: int,
-                 head_gate: Optional[torch.Tensor] = None) -> None:
+                 head_gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                 sink: Optional[torch.Tensor] = None) -> None:
     """The plain kernel: float32 arithmetic; keys of ``k_dim``, values of ``v_dim`` elements at
     ``v_cache`` with rows ``v_row_stride`` apart (the key cache itself for values that are a
-    prefix of the keys); ``head_gate`` [T, >= H]: head h's row times sigmoid(head_gate[t, h])."""
+    prefix of the keys); ``head_gate`` [T, >= H]: head h's row times sigmoid(head_gate[t, h]);
+    ``softcap`` > 0: a scaled score s becomes softcap tanh(s / softcap); ``sink`` float32 [H]: its
+    exponential joins the softmax's denominator."""
     tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads, attention_kv_tile_rows())
     fn = getattr(L.core(), "slb_attention_kv_" + _suffix(q.dtype))
     L.check(fn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), v_row_stride,
@@ -917,7 +945,7 @@ def attention_kv(ctx, q, k_cache, v_cache, v_row_stride: int, out, block_table, 
                ctx.cu_q.data_ptr(), ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n,
                num_heads, num_kv_heads, k_dim, v_dim, page_size, k_cache.shape[0], float(scale),
                int(window), _p(head_gate), head_gate.stride(0) if head_gate is not None else 0,
-               _stream()), "attention_kv")
+               float(softcap), _p(sink), _stream()), "attention_kv")
 
 
 def attention_kv_splits(num_seqs: int, num_kv_heads: int, longest_context: int, window: int,
@@ -950,10 +978,11 @@ def attention_kv_resident(lib, k_dim: int, v_dim: int, narrow: bool, group: int)
 
 def attention_kv_mma(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num_heads: int,
                      num_kv_heads: int, k_dim: int, v_dim: int, page_size: int, scale: float, window: int,
-                     head_gate: Optional[torch.Tensor] = None) -> None:
+                     head_gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                     sink: Optional[torch.Tensor] = None) -> None:
     """The tensor-core kernel (bfloat16), for prompt portions and single tokens; in a step of
     single tokens the keys of a request are split over several blocks when the requests alone
-    would not fill the device."""
+    would not fill the device.  ``softcap`` and ``sink`` as in ``attention_kv``."""
     lib = L.attention_kv(k_dim, v_dim)
     rows = lib.slb_attention_kv_mma_tile_rows()
     tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads, rows)
@@ -968,14 +997,17 @@ def attention_kv_mma(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num
             T = q.shape[0]
             part_o = torch.empty((T, num_heads, splits, v_dim), dtype=_F32, device=q.device)
             part_ml = torch.empty((T, num_heads, splits, 2), dtype=_F32, device=q.device)
-    L.check(lib.slb_attention_kv_mma_bf16(
-        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), 1 if tied else 0, out.data_ptr(),
-        out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
-        ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads,
-        page_size, k_cache.shape[0], float(scale), int(window), _p(head_gate),
-        head_gate.stride(0) if head_gate is not None else 0, splits, _p(part_o), _p(part_ml),
-        1 if ctx.decode_only and attention_kv_narrow and num_heads // num_kv_heads <= 16 else 0, _stream()),
-        "attention_kv_mma")
+    args = (q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), 1 if tied else 0, out.data_ptr(),
+            out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
+            ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads,
+            page_size, k_cache.shape[0], float(scale), int(window), _p(head_gate),
+            head_gate.stride(0) if head_gate is not None else 0, splits, _p(part_o), _p(part_ml),
+            1 if ctx.decode_only and attention_kv_narrow and num_heads // num_kv_heads <= 16 else 0)
+    if softcap or sink is not None:
+        L.check(lib.slb_attention_kv_mma_capped_bf16(*args, float(softcap or 0.0), _p(sink), _stream()),
+                "attention_kv_mma")
+        return
+    L.check(lib.slb_attention_kv_mma_bf16(*args, _stream()), "attention_kv_mma")
 
 
 attention_kv_split = True      # (off: one block a request and kv head, the twin)
@@ -1175,12 +1207,19 @@ def moe_route_scored(logits: torch.Tensor, groups: int, keep: int, top: int, rou
     return ids, weights
 
 
-GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
 
 
-def gated_act(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, activation: str = "silu") -> None:
-    """out[t, i] = act(gate_i) * up_i (layout as ``swiglu``); ``activation`` "silu" or "gelu_tanh"
-    (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))))."""
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, activation: str = "silu",
+              limit: Optional[float] = None, alpha: float = 1.0) -> None:
+    """out[t, i] = act(gate_i) * up_i (layout as ``swiglu``); ``activation`` "silu", "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))) or "swish_clamped": with g = min(gate, limit)
+    and u = clamp(up, -limit, limit), out = g sigmoid(alpha g) (u + 1)."""
+    if activation == "swish_clamped":
+        fn = getattr(L.core(), "slb_gated_act_clamped_" + _suffix(out.dtype))
+        L.check(fn(gate_up.data_ptr(), out.data_ptr(), out.shape[0], out.shape[1], gate_up.stride(0),
+                   out.stride(0), int(block), float(limit), float(alpha), _stream()), "gated_act")
+        return
     fn = getattr(L.core(), "slb_gated_act_" + _suffix(out.dtype))
     L.check(fn(gate_up.data_ptr(), out.data_ptr(), out.shape[0], out.shape[1], gate_up.stride(0),
                out.stride(0), int(block), GATED_ACTIVATIONS[activation], _stream()), "gated_act")
@@ -1217,6 +1256,24 @@ def hyper_mix_norm(streams: torch.Tensor, update: Optional[torch.Tensor], mix: O
                out.stride(0) if out is not None else 0, _p(row_map), rows, n, w, _stream()), "hyper_mix_norm")
 
 
+def rms_norm_rows(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out: torch.Tensor) -> None:
+    """out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * weight over the columns of ``x`` [T, n] (a view with any
+    row stride: a latent inside a wider projection); float32 arithmetic."""
+    fn = getattr(L.core(), "slb_rms_norm_rows_" + _suffix(x.dtype))
+    L.check(fn(x.data_ptr(), x.stride(0), _p(weight), float(eps), out.data_ptr(), out.stride(0), x.shape[0],
+               x.shape[1], _stream()), "rms_norm_rows")
+
+
+def norm_sum2(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float, factor: float,
+              out: torch.Tensor) -> None:
+    """out = factor (rmsnorm(a) wa + rmsnorm(b) wb) row by row; a, b float32 [T, n]."""
+    if a.dtype != _F32 or b.dtype != _F32:
+        raise L.KernelError("norm_sum2 takes float32 branches")
+    fn = getattr(L.core(), "slb_norm_sum2_" + _suffix(out.dtype))
+    L.check(fn(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), wa.data_ptr(), wb.data_ptr(), float(eps),
+               float(factor), out.data_ptr(), out.stride(0), a.shape[0], a.shape[1], _stream()), "norm_sum2")
+
+
 GATE_ACTIVATIONS = {None: 0, "sigmoid": 1, "silu": 2}
 
 
@@ -1244,6 +1301,8 @@ class _DecayAttnArgs(_ct.Structure):
         ("positions", _ct.c_void_p), ("cu_q", _ct.c_void_p), ("state_slots", _ct.c_void_p),
         ("state", _ct.c_void_p), ("num_slots", _ct.c_int),
         ("out", _ct.c_void_p), ("ldo", _ct.c_int),
+        ("gate_z", _ct.c_void_p), ("ld_gate", _ct.c_int), ("gate_bias", _ct.c_void_p),
+        ("gate_inv_tau", _ct.c_float), ("q_scale", _ct.c_float), ("state_stride", _ct.c_longlong),
     ]
 
 
@@ -1265,24 +1324,35 @@ def decay_attention_max_dim() -> int:
     return L.core().slb_decay_attention_max_dim()
 
 
-def decay_attention(proj: torch.Tensor, ctx, state: torch.Tensor, decay: torch.Tensor, out: torch.Tensor, *,
+def decay_attention(proj: torch.Tensor, ctx, state: torch.Tensor, decay: Optional[torch.Tensor], out: torch.Tensor, *,
                     q_off: int, k_off: int, v_off: int, num_heads: int, head_dim: int, value_dim: int,
                     activation: Optional[str] = None, freq: Optional[torch.Tensor] = None, rot_dims: int = 0,
-                    key_scale: float = 1.0) -> None:
+                    key_scale: float = 1.0, query_scale: float = 1.0, gate_z: Optional[torch.Tensor] = None,
+                    gate_bias: Optional[torch.Tensor] = None, gate_tau: float = 1.0) -> None:
     """o_t = S_t^T q_t with S_t = decay_h S_{t-1} + k_t v_t^T per head over the tokens of every request
     of the step, in order; q, k, v are columns of ``proj`` [T, ...]; ``state`` float32
-    [slots, H, D, Dv] is read at ``ctx.state_slots`` and left advanced; ``out`` float32 [T, H * Dv]."""
+    [slots, H, D, Dv] (or [slots, >= H * D * Dv]: a slice of a larger record) is read at
+    ``ctx.state_slots`` and left advanced; ``out`` float32 [T, H * Dv].  With ``gate_z`` (float32
+    [T, H * D]; ``decay`` None) every key channel of every token has its own decay
+    sigmoid(gate_z + gate_bias)^(1 / gate_tau): S_t = diag(alpha_t) S_{t-1} + k_t v_t^T."""
     a = _DecayAttnArgs()
     a.proj, a.ld = proj.data_ptr(), proj.stride(0)
     a.q_off, a.k_off, a.v_off = q_off, k_off, v_off
     a.H, a.D, a.Dv = num_heads, head_dim, value_dim
     a.act = {None: 0, "silu": 1}[activation]
     a.freq, a.rot_dims, a.k_scale = _p(freq), rot_dims, float(key_scale)
-    a.decay = decay.data_ptr()
+    a.decay = _p(decay)
     a.positions, a.cu_q, a.state_slots = ctx.positions.data_ptr(), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr()
     a.state, a.num_slots = state.data_ptr(), state.shape[0]
     a.out, a.ldo = out.data_ptr(), out.stride(0)
-    if (decay_attention_chunked and proj.dtype == torch.bfloat16 and not ctx.decode_only
+    a.gate_z, a.ld_gate = _p(gate_z), (gate_z.stride(0) if gate_z is not None else 0)
+    a.gate_bias, a.gate_inv_tau, a.q_scale = _p(gate_bias), 1.0 / float(gate_tau), float(query_scale)
+    a.state_stride = state.stride(0)
+    if gate_z is not None and gate_z.dtype != _F32:
+        raise L.KernelError("decay_attention: the decays' logits must be float32")
+    plain = (gate_z is None and query_scale == 1.0
+             and state.stride(0) == num_heads * head_dim * value_dim)
+    if (decay_attention_chunked and plain and proj.dtype == torch.bfloat16 and not ctx.decode_only
             and head_dim <= L.core().slb_decay_chunk_max_dim()
             and ctx.num_tokens >= decay_attention_chunk_min_tokens * ctx.num_seqs):
         # portions of prompts: the chunked form on the tensor cores

@@ -41,8 +41,8 @@ _CORE_SIGNATURES = {
     "slb_mix_heads_gate_bf16": [P, P, I, I, P, I, P, P, I, P, I, I, I, I, I, P],
     "slb_dyt_add_norm_f32": [P, I, P, I, P, P, P, P, P, P, P, I, P, I, I, P],
     "slb_dyt_add_norm_bf16": [P, I, P, I, P, P, P, P, P, P, P, I, P, I, I, P],
-    "slb_qk_conv_cache_f32": [P, I, P, I, P, P, P, P, P, P, I, I, I, F, I, P, I, P, I, I, I, I, I, I, P],
-    "slb_qk_conv_cache_bf16": [P, I, P, I, P, P, P, P, P, P, I, I, I, F, I, P, I, P, I, I, I, I, I, I, P],
+    "slb_qk_conv_cache_f32": [P, I, P, I, P, P, P, P, P, P, I, I, I, F, I, P, I, P, I, I, I, I, I, I, LL, P],
+    "slb_qk_conv_cache_bf16": [P, I, P, I, P, P, P, P, P, P, I, I, I, F, I, P, I, P, I, I, I, I, I, I, LL, P],
     "slb_conv_cache_status": [I],
     "slb_paged_attention_generic_status": [I],
     "slb_paged_attention_generic_tile_rows": [],
@@ -69,8 +69,8 @@ _CORE_SIGNATURES = {
     "slb_sigmoid_gate_bf16": [P, I, P, I, P, I, I, I, I, P],
     "slb_attention_kv_tile_rows": [],
     "slb_attention_kv_status": [I],
-    "slb_attention_kv_f32": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, P],
-    "slb_attention_kv_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, P],
+    "slb_attention_kv_f32": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, F, P, P],
+    "slb_attention_kv_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, F, P, P],
     "slb_gemm_simt_batched_f32": [P, I, P, I, P, I, I, I, I, I, LL, LL, LL, P],
     "slb_gemm_simt_batched_bf16": [P, I, P, I, P, I, I, I, I, I, LL, LL, LL, P],
     "slb_moe_tile_rows": [],
@@ -78,6 +78,12 @@ _CORE_SIGNATURES = {
     "slb_moe_route_scored": [P, I, I, I, I, I, I, F, I, I, P, I, F, P, P, P],
     "slb_gated_act_f32": [P, P, I, I, I, I, I, I, P],
     "slb_gated_act_bf16": [P, P, I, I, I, I, I, I, P],
+    "slb_gated_act_clamped_f32": [P, P, I, I, I, I, I, F, F, P],
+    "slb_gated_act_clamped_bf16": [P, P, I, I, I, I, I, F, F, P],
+    "slb_rms_norm_rows_f32": [P, I, P, F, P, I, I, I, P],
+    "slb_rms_norm_rows_bf16": [P, I, P, F, P, I, I, I, P],
+    "slb_norm_sum2_f32": [P, I, P, I, P, P, F, F, P, I, I, I, P],
+    "slb_norm_sum2_bf16": [P, I, P, I, P, P, F, F, P, I, I, I, P],
     "slb_attention_kv_maps_f32": [P, I, P, I, I, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
     "slb_attention_kv_maps_bf16": [P, I, P, I, I, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
     "slb_hyper_max_streams": [],
@@ -257,6 +263,8 @@ _ATTN_KV_SIGNATURES = {
     "slb_attention_kv_mma_tile_rows": [],
     "slb_attention_kv_mma_status": [I],
     "slb_attention_kv_mma_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P, I, I, P, P, I, P],
+    "slb_attention_kv_mma_capped_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P, I, I, P, P, I,
+                                         F, P, P],
     "slb_attention_kv_mma_max_splits": [],
     "slb_attention_kv_mma_resident": [I, I],
     "slb_attention_kv_mma_maps_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P, P, I, P],

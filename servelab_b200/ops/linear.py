@@ -121,7 +121,8 @@ def qkv_projection(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Te
                      rotary_dim, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim)
 
 
-def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int, activation: str = "silu") -> torch.Tensor:
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int, activation: str = "silu",
+                 limit: Optional[float] = None, alpha: float = 1.0) -> torch.Tensor:
     """act(x Wg^T) * (x Wu^T) (``activation`` "silu" or "gelu_tanh"; the product's own epilogue
     knows SiLU only) for ``w_gate_up`` [2I, h]: gate rows then up rows
     (``block`` 0), or alternating in runs of ``block`` rows.  Decode steps in bfloat16
@@ -140,7 +141,7 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int, activatio
     if activation == "silu":
         K.swiglu(gu, act, block)
     else:
-        K.gated_act(K.plain_unless(None, gu), act, block, activation)
+        K.gated_act(K.plain_unless(None, gu), act, block, activation, limit, alpha)
     return act
 
 

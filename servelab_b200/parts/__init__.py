@@ -1,7 +1,7 @@
 """Parts that layers are put together from; importing registers the built-in kinds."""
 
 from . import (attention, block, conv_attention, decay_attention, differential_attention,  # noqa: F401
-               feed_forward, latent_attention, norm, normed_attention, position,
+               feed_forward, latent_attention, norm, normed_attention, parallel_mixers, position,
                routed_experts)                                                  # (registration)
 from .base import (Block, BuildEnv, FeedForward, LayerCache, Mixer, Norm, Part,
                    PositionEncoding)

@@ -28,6 +28,8 @@ class GatedMLP(FeedForward):
                              f"({', '.join(K.GATED_ACTIVATIONS)})")
         if spec.bias:
             raise ValueError("gated_mlp: biases are not supported")
+        if spec.activation == "swish_clamped" and not (spec.limit is not None and spec.limit > 0):
+            raise ValueError("gated_mlp: the clamped activation needs a positive limit")
 
     @classmethod
     def declare(cls, spec, prefix):
@@ -52,5 +54,6 @@ class GatedMLP(FeedForward):
         self.w_down = store.get(f"{self.prefix}.{self.spec.down_name}{sfx}")
 
     def forward(self, ctx, x):
-        act = gated_linear(x, self.w_gate_up, self.block, self.spec.activation)
+        act = gated_linear(x, self.w_gate_up, self.block, self.spec.activation, self.spec.limit,
+                           self.spec.swish_alpha)
         return linear(act, self.w_down, consumer="norm")

@@ -30,6 +30,8 @@ class RMSNorm(Norm):
 
     def load(self, store):
         self.weight = store.get(self.prefix + self.spec.weight_suffix)
+        if self.spec.unit_offset:             # the stored weight lies around zero: the factor is 1 + w
+            self.weight = (self.weight.to(torch.float32) + 1.0).contiguous()
 
     def read_streams(self, ctx, streams, pending, read_weights, out_rows=None):
         """For a residual kept as streams [T, n, dim]: folds the pending update in (``HyperPending``

@@ -17,6 +17,18 @@ from .base import PositionEncoding
 from .registry import register_position
 
 
+def stretch_long_wavelengths(f: torch.Tensor, factor: float, low: float, high: float,
+                             original: float) -> torch.Tensor:
+    """Frequencies ``f`` (float64) with the long wavelengths stretched: with l = 2 pi / f, a frequency
+    with l > original / low becomes f / factor, one with l < original / high stays, and between the
+    two s = (original / l - low) / (high - low) blends them, (1 - s) f / factor + s f."""
+    wavelength = 2.0 * math.pi / f
+    s = ((original / wavelength - low) / (high - low)).clamp(0.0, 1.0)
+    blended = (1.0 - s) * f / factor + s * f
+    return torch.where(wavelength < original / high, f,
+                       torch.where(wavelength > original / low, f / factor, blended))
+
+
 @register_position("rotary")
 class RotaryEmbedding(PositionEncoding):
     graph_safe = True
@@ -27,6 +39,15 @@ class RotaryEmbedding(PositionEncoding):
         if rd % 2 or rd > spec.head_dim:
             raise ValueError(f"rotary_dim {rd} must be even and <= head_dim {spec.head_dim}")
         inv_freq = 1.0 / (spec.theta ** (torch.arange(0, rd, 2, dtype=torch.float32) / rd))
+        if spec.precise or spec.stretch_factor is not None:
+            f = float(spec.theta) ** (-2.0 * torch.arange(rd // 2, dtype=torch.float64) / rd)
+            if spec.stretch_factor is not None:
+                if not (spec.stretch_factor > 0 and spec.stretch_high > spec.stretch_low >= 0
+                        and spec.stretch_original > 0):
+                    raise ValueError("rotary: a stretch needs factor > 0, high > low >= 0 and original > 0")
+                f = stretch_long_wavelengths(f, float(spec.stretch_factor), float(spec.stretch_low),
+                                             float(spec.stretch_high), float(spec.stretch_original))
+            inv_freq = f.to(torch.float32)
         self.rotary_dim = rd
         self.inv_freq = inv_freq.to(env.device)
 
@@ -60,6 +81,9 @@ class PairRotary(PositionEncoding):
             ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
             f = f / factor * ramp + f * (1.0 - ramp)
             self.magnitude = 0.1 * math.log(factor) + 1.0
+        if spec.stretch_factor is not None:
+            f = stretch_long_wavelengths(f, float(spec.stretch_factor), float(spec.stretch_low),
+                                         float(spec.stretch_high), float(spec.stretch_original))
         self.dims = d
         self.freq = f.to(torch.float32).to(env.device)
 

@@ -177,6 +177,9 @@ class RandomSource(WeightSource):
 
     def read(self, name):
         d = self.decls[name]
+        if any(n < 0 for n in d.shape):
+            raise ValueError(f"{name}: a size that the checkpoint decides cannot be drawn at random; "
+                             f"the configuration must give it")
         gen = torch.Generator(device=self.device)
         gen.manual_seed((self.seed * 0x9E3779B1 + zlib.crc32(name.encode())) % (2 ** 63))
         if d.role == TABLE:
@@ -205,7 +208,9 @@ def check_source(source: WeightSource, decls: Iterable[TensorDecl],
         n for n in have
         if n not in want and n not in optional
         and not any(n.endswith(s) for s in ignored_suffixes))
+    def differs(got, asked) -> bool:          # (a declared size of -1 is read from the tensor)
+        return len(got) != len(asked) or any(a != -1 and a != g for g, a in zip(got, asked))
     wrong = sorted((n, source.shape(n), want[n]) for n in want
-                   if n in have and tuple(source.shape(n)) != want[n])
+                   if n in have and differs(tuple(source.shape(n)), want[n]))
     if missing or unexpected or wrong:
         raise WeightsError(source.where, missing, unexpected, wrong)
