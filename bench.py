@@ -20,7 +20,7 @@ extra flush is needed.
 ``--impl reference``: the reference's engine cannot run (the line says what its import
 raises); its two GPU kernels can, and are timed beside this package's on the same data.
 
-``--compare dezelorn`` / ``--compare daferax`` / ``--compare zimupel``: instead of all this, the named
+``--compare dezelorn`` / ``--compare daferax`` / ``--compare zimupel`` / ``--compare sumolorn``: instead of all this, the named
 design beside the Qwen2 decoder (Zimupel: beside Daferax) at a few equal layer sizes (prefill and decode throughput, the times and roofline
 fractions of the kernels that differ), one JSON line.
 
@@ -175,7 +175,7 @@ def main(argv=None) -> int:
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="profiling aid: run only the decode loop or only the prefill")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch kernels eagerly")
-    ap.add_argument("--compare", default="", choices=["", "dezelorn", "daferax", "zimupel"],
+    ap.add_argument("--compare", default="", choices=["", "dezelorn", "daferax", "zimupel", "sumolorn"],
                     help="instead of the default workload: prefill and decode throughput of the named "
                          "design beside the Qwen2 decoder at equal layer sizes (bench/arch_compare.py)")
     ap.add_argument("--compare-sizes", default="", help="comma-separated subset of the sizes to compare")

@@ -280,6 +280,127 @@ def _zimupel_rooflines(size, res, peaks) -> Dict[str, object]:
     return out
 
 
+# Sumolorn: four layers -- soft-capped windowed attention with sinks, a parallel layer (convolved
+# windowed attention beside a linear attention with learned decays), a latent attention with latent
+# queries, the windowed attention again -- each with the clamped feed-forward.  Beside it the closest
+# model the package has: Daferax with a grouped-query attention where Sumolorn has its attention and
+# its parallel layer, a latent attention where it has one, and a dense feed-forward of the same size.
+# width, heads, kv heads, head size, feed-forward, latent size, rotated part, queries' latent,
+# heads / key size / value size of the linear branch
+SUMOLORN_SIZES = {
+    "1b-like": (2048, 16, 4, 128, 5632, 256, 64, 768, 8, 128, 256),
+    "small-1024": (1024, 8, 2, 64, 2816, 192, 64, 384, 4, 64, 128),
+}
+
+
+def sumolorn_config(width, heads, kv, dim, ff, rank, rot, q_rank, lh, ld, lv, layers=LAYERS) -> dict:
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    attn = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
+            "mask": {"size": WINDOW},
+            "rot": {"base": 2000000.0, "dims": dim,
+                    "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    left = {"conv": 4, "heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+            "mask": {"size": WINDOW}, "rot": {"base": 400000.0, "dims": dim // 2}}
+    right = {"heads": lh, "dim": ld, "vdim": lv, "tau": 8.0, "rank": 32}
+    latent = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank, "q_rank": q_rank,
+              "scale": (dim + rot) ** -0.5, "rot": {"base": 100000.0, "dims": rot}}
+    kinds = [("attention", attn), ("parallel", {"left": left, "right": right}), ("latent_attention", latent),
+             ("attention", attn)]
+    return {"architecture": "Sumolorn", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(layers)]}
+
+
+def daferax_like_sumolorn(width, heads, kv, dim, ff, rank, rot, q_rank, lh, ld, lv, layers=LAYERS) -> dict:
+    mlp = {"kind": "dense", "ff": ff}
+    attn = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+            "mask": {"size": WINDOW}, "rot": {"base": 1000000.0, "dims": dim}}
+    latent = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank,
+              "scale": (dim + rot) ** -0.5, "rot": {"base": 250000.0, "dims": rot}}
+    kinds = [("attention", attn), ("attention", attn), ("latent_attention", latent), ("attention", attn)]
+    return {"architecture": "Daferax", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5},
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(layers)]}
+
+
+def _sumolorn_rooflines(size, res, peaks) -> Dict[str, object]:
+    """Microseconds per launch and achieved fractions of the measured peaks for the kernels of the
+    Sumolorn layers beside their Daferax counterparts, from the eager profiles.  Softmax attention,
+    prefill: 2 (Dk + Dv) flops per visible pair and head of the bf16 peak (for the latent form, what
+    the absorbed form multiplies); decode: the cached rows 8 requests may see, of the copy bandwidth.
+    Linear attention, prefill: 4 T H D Dv flops (the recurrence's own arithmetic); decode: the state
+    read and written once.  Elementwise kernels: the bytes they must move, of the copy bandwidth."""
+    width, heads, kv, dim, ff, rank, rot, q_rank, lh, ld, lv = SUMOLORN_SIZES[size]
+    out: Dict[str, object] = {}
+    sp, sd = res["sumolorn"]["prefill_kernels_us"], res["sumolorn"]["decode_b8_kernels_us"]
+    dp, dd = res["daferax"]["prefill_kernels_us"], res["daferax"]["decode_b8_kernels_us"]
+    win_pairs = sum(min(t + 1, WINDOW) for t in range(PROMPT))
+    full_pairs = PROMPT * (PROMPT + 1) / 2
+
+    def hbm(nbytes, us):
+        return round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+
+    def tf(flops, us):
+        return round(flops / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
+
+    def total(table, *names):
+        return sum(table.get(n) or 0 for n in names)
+
+    # prefill attention, all softmax layers of a model together (the kernels' names do not tell the layers apart)
+    s_flops = (3 * win_pairs * heads * 4 * dim) + full_pairs * heads * 2 * (2 * rank + rot)
+    d_flops = (3 * win_pairs * heads * 4 * dim) + full_pairs * heads * 2 * (2 * rank + rot)
+    s_att = total(sp, "attention_kv_mma", "attention_kv_tc", "attention_kv", "prefill_attention_tc", "prefill_attention")
+    d_att = total(dp, "attention_kv_mma", "attention_kv_tc", "attention_kv", "prefill_attention_tc", "prefill_attention")
+    if s_att and d_att:
+        out["prefill_softmax_attention_us_all_layers"] = {"sumolorn": round(s_att, 1), "daferax": round(d_att, 1)}
+        out["prefill_softmax_attention_bf16_frac"] = {"sumolorn": tf(s_flops, s_att), "daferax": tf(d_flops, d_att)}
+    rows = 8 * (3 * min(CONTEXT, WINDOW) * kv * 2 * dim + CONTEXT * (rank + rot)) * 2
+    s_dec = total(sd, "attention_kv_mma", "attention_kv", "decode_attention")
+    d_dec = total(dd, "attention_kv_mma", "attention_kv", "decode_attention")
+    if s_dec and d_dec:
+        out["decode_b8_softmax_attention_us_all_layers"] = {"sumolorn": round(s_dec, 2), "daferax": round(d_dec, 2)}
+        out["decode_b8_softmax_attention_hbm_frac"] = {"sumolorn": hbm(rows, s_dec), "daferax": hbm(rows, d_dec)}
+    if sp.get("decay_attention"):
+        us = sp["decay_attention"]
+        out["sumolorn_linear_prefill_us"] = round(us, 1)
+        out["sumolorn_linear_prefill_bf16_frac"] = tf(4.0 * PROMPT * lh * ld * lv, us)
+    if sd.get("decay_attention"):
+        us = sd["decay_attention"]
+        out["sumolorn_linear_decode_b8_us"] = round(us, 2)
+        out["sumolorn_linear_decode_b8_hbm_frac"] = hbm(8 * lh * ld * lv * 4 * 2, us)
+    if sp.get("short_conv"):
+        us = sp["short_conv"]
+        chans = (heads + 2 * kv) * dim
+        out["sumolorn_conv_us"], out["sumolorn_conv_hbm_frac"] = round(us, 2), hbm(PROMPT * chans * 4, us)
+    if sp.get("norm_sum2"):
+        us = sp["norm_sum2"]
+        out["sumolorn_branch_norms_us"], out["sumolorn_branch_norms_hbm_frac"] = round(us, 2), hbm(PROMPT * width * 10, us)
+    if sp.get("head_prep"):
+        us = sp["head_prep"] / 5                # (three grouped layers, and two launches of the latent layer)
+        out["sumolorn_head_prep_us"] = round(us, 2)
+        moved = PROMPT * 4 * (3 * (heads + 2 * kv) * dim + heads * (dim + rot) + rank + rot) / 5
+        out["sumolorn_head_prep_hbm_frac"] = hbm(moved, us)
+    if dp.get("head_prep"):
+        us = dp["head_prep"] / LAYERS
+        out["daferax_head_prep_us"] = round(us, 2)
+        moved = PROMPT * 4 * (3 * (heads + 2 * kv) * dim + heads * (dim + rot) + rank + rot) / LAYERS
+        out["daferax_head_prep_hbm_frac"] = hbm(moved, us)
+    if sp.get("add_rmsnorm"):
+        us = sp["add_rmsnorm"] / (2 * LAYERS + 1)
+        out["sumolorn_norm_us"], out["sumolorn_norm_hbm_frac"] = round(us, 2), hbm(PROMPT * 12 * width, us)
+    if dp.get("ln_add_norm"):
+        us = dp["ln_add_norm"] / (2 * LAYERS + 1)
+        out["daferax_norm_us"], out["daferax_norm_hbm_frac"] = round(us, 2), hbm(PROMPT * 12 * width, us)
+    if sp.get("gated_act"):
+        us = sp["gated_act"] / LAYERS
+        out["sumolorn_activation_us"], out["sumolorn_activation_hbm_frac"] = round(us, 2), hbm(PROMPT * ff * 6, us)
+    if dp.get("swiglu"):
+        us = dp["swiglu"] / LAYERS
+        out["daferax_activation_us"], out["daferax_activation_hbm_frac"] = round(us, 2), hbm(PROMPT * ff * 6, us)
+    for name in ("group_norm_gate", "rms_norm_rows", "sigmoid_gate"):
+        if sp.get(name) or dp.get(name):
+            out[f"prefill_{name}_us"] = {"sumolorn": round(sp.get(name) or 0, 2), "daferax": round(dp.get(name) or 0, 2)}
+    return out
+
+
 def _measure(cfg: dict, note) -> Dict[str, object]:
     import torch
     from ..ops import kernels as K
@@ -400,6 +521,23 @@ def _kernel_rooflines(size, res: Dict[str, Dict[str, object]], peaks) -> Dict[st
 
 
 def run(peaks, note=lambda m: None, sizes=None, design: str = "dezelorn") -> Dict[str, object]:
+    if design == "sumolorn":
+        result = {"compare": "sumolorn vs daferax (grouped-query and latent attention, dense feed-forward) at equal "
+                             "layer sizes", "layers": LAYERS, "prompt": PROMPT, "decode_context": CONTEXT,
+                  "window": WINDOW, "vocab": VOCAB, "dtype": "bf16",
+                  "data": "synthetic: random weights, token ids uniform over the vocabulary",
+                  "peaks": peaks.get("source"), "sizes": {}}
+        for size in (sizes or SUMOLORN_SIZES):
+            dims = SUMOLORN_SIZES[size]
+            res = {}
+            for arch, make in (("sumolorn", sumolorn_config), ("daferax", daferax_like_sumolorn)):
+                note(f"{size}: {arch}")
+                res[arch] = _measure(make(*dims), note)
+            res["kernels"] = _sumolorn_rooflines(size, res, peaks)
+            res["dims"] = dict(zip(("width", "heads", "kv_heads", "head_dim", "ff", "kv_rank", "rot_dim", "q_rank",
+                                    "linear_heads", "linear_key_dim", "linear_value_dim"), dims))
+            result["sizes"][size] = res
+        return result
     if design == "zimupel":
         result = {"compare": "zimupel vs daferax (grouped-query attention in every layer) at equal layer sizes",
                   "layers": LAYERS, "prompt": PROMPT, "decode_context": CONTEXT, "vocab": VOCAB, "dtype": "bf16",

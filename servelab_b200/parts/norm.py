@@ -26,7 +26,8 @@ class RMSNorm(Norm):
 
     @classmethod
     def declare(cls, spec, prefix):
-        return [TensorDecl(prefix + spec.weight_suffix, (spec.dim,), NORM)]
+        # (a weight stored around zero is drawn around zero in random models: the role of a bias)
+        return [TensorDecl(prefix + spec.weight_suffix, (spec.dim,), BIAS if spec.unit_offset else NORM)]
 
     def load(self, store):
         self.weight = store.get(self.prefix + self.spec.weight_suffix)
