@@ -33,7 +33,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--compiler-options", "-fPIC",
 
 CORE_SOURCES = ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_simt.cu",
                 "sampling.cu", "gemm_tcgen05.cu", "dynamic_tanh.cu", "short_conv.cu", "layernorm.cu",
-                "head_prep.cu", "attention_kv.cu", "moe.cu", "hyper.cu", "decay_attention.cu", "decay_attention_mma.cu"]
+                "head_prep.cu", "attention_kv.cu", "moe.cu", "hyper.cu", "decay_attention.cu", "decay_attention_mma.cu",
+                "decay_gated_chunk.cu"]
 HEADERS = ["common.cuh", "no_alloc.h", "mma_util.cuh", "tma_util.cuh", "decay_attention.cuh"]
 
 _lock = threading.Lock()

@@ -1311,6 +1311,18 @@ class _DecayChunkArgs(_ct.Structure):
                 ("num_tiles", _ct.c_int), ("work", _ct.c_void_p)]
 
 
+class _GatedChunkArgs(_ct.Structure):
+    _fields_ = [("a", _DecayAttnArgs), ("tile_seq", _ct.c_void_p), ("tile_row0", _ct.c_void_p),
+                ("num_tiles", _ct.c_int), ("work", _ct.c_void_p), ("logs", _ct.c_void_p), ("dtot", _ct.c_void_p),
+                ("scores", _ct.c_void_p)]
+
+
+# Learned decays: steps that bring portions of prompts in bfloat16 take the chunked kernels (float32
+# arithmetic on the CUDA cores, chunks of 32 tokens) from the same number of tokens a request on.
+decay_gated_chunked = True
+force_gated_chunks = False       # (tests: the chunked kernels also for float32 rows)
+
+
 # Steps that bring portions of prompts in bfloat16 take the chunked tensor-core kernels when the
 # step has at least this many tokens a request (shorter portions: the recurrent kernel, which is
 # also the float32 path and the one for steps of single tokens).
@@ -1352,6 +1364,25 @@ def decay_attention(proj: torch.Tensor, ctx, state: torch.Tensor, decay: Optiona
         raise L.KernelError("decay_attention: the decays' logits must be float32")
     plain = (gate_z is None and query_scale == 1.0
              and state.stride(0) == num_heads * head_dim * value_dim)
+    if (gate_z is not None and not ctx.decode_only and head_dim <= L.core().slb_decay_gated_chunk_max_dim()
+            and ctx.num_tokens >= decay_attention_chunk_min_tokens * ctx.num_seqs
+            and (force_gated_chunks or (decay_gated_chunked and proj.dtype == torch.bfloat16))):
+        chunk = L.core().slb_decay_gated_chunk_tokens()
+        tile_seq, tile_row0, n = ctx.attention_tiles(1, chunk)
+        c = _GatedChunkArgs()
+        c.a = a
+        c.tile_seq, c.tile_row0, c.num_tiles = tile_seq.data_ptr(), tile_row0.data_ptr(), n
+        dev = proj.device
+        work = torch.empty((max(n, 1), num_heads, head_dim, value_dim), dtype=_F32, device=dev)
+        logs = torch.empty((proj.shape[0], num_heads * head_dim), dtype=_F32, device=dev)
+        dtot = torch.empty((max(n, 1), num_heads, head_dim), dtype=_F32, device=dev)
+        scores = torch.empty((max(n, 1), num_heads, chunk, chunk), dtype=_F32, device=dev)
+        c.work, c.logs, c.dtot, c.scores = work.data_ptr(), logs.data_ptr(), dtot.data_ptr(), scores.data_ptr()
+        fn = getattr(L.core(), "slb_decay_gated_chunk_" + _suffix(proj.dtype))
+        L.check(fn(_ct.byref(c), ctx.num_seqs, _stream()), "decay_attention (gated chunks)")
+        global launch_count
+        launch_count += 3
+        return
     if (decay_attention_chunked and plain and proj.dtype == torch.bfloat16 and not ctx.decode_only
             and head_dim <= L.core().slb_decay_chunk_max_dim()
             and ctx.num_tokens >= decay_attention_chunk_min_tokens * ctx.num_seqs):

@@ -99,6 +99,10 @@ _CORE_SIGNATURES = {
     "slb_decay_chunk_max_dim": [],
     "slb_decay_chunk_tokens": [],
     "slb_decay_chunk_bf16": [P, I, I, P],
+    "slb_decay_gated_chunk_max_dim": [],
+    "slb_decay_gated_chunk_tokens": [],
+    "slb_decay_gated_chunk_f32": [P, I, P],
+    "slb_decay_gated_chunk_bf16": [P, I, P],
     "slb_router_logits_f32": [P, I, P, I, P, I, I, I, I, P],
     "slb_router_logits_bf16": [P, I, P, I, P, I, I, I, I, P],
     "slb_moe_plan_ints": [I, I],

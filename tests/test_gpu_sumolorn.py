@@ -328,8 +328,11 @@ def _run_gated(K, proj, z, bias, state, Hh, D, Dv, pieces, tau, qscale):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(3, 8, 12, 4.0), (2, 40, 64, 12.0), (1, 24, 40, 1.0), (2, 136, 33, 2.0)])
-def test_learned_decays_whole_in_portions_and_token_by_token(dtype, shape):
+def test_learned_decays_whole_in_portions_and_token_by_token(dtype, shape, monkeypatch):
+    """The token-by-token kernel (the float32 path, and every step of single tokens): its results
+    do not depend on the cut, bit for bit."""
     from servelab_b200.ops import kernels as K
+    monkeypatch.setattr(K, "decay_gated_chunked", False)
     Hh, D, Dv, tau = shape
     lens = [41, 7]
     proj, z, bias = _gated_case(31, Hh, D, Dv, sum(lens), dtype)
@@ -376,6 +379,69 @@ def test_learned_decays_keep_or_forget_a_key_from_far_back():
     state = torch.zeros(1, Hh * D * Dv, device=DEV)
     out = _run_gated(K, proj.to(DEV), z.to(DEV), bias.to(DEV), state, Hh, D, Dv,
                      [[(0, 0, 700)], [(0, 700, 1)], [(0, 701, 799)], [(0, 1500, 1)]], 2.0, 1.0)
+    last = out[T - 1].cpu().view(Hh, Dv)
+    assert (last[0] - 5.0 * D).abs().max() < 1e-2 and last[1].abs().max() < 1e-6
+
+
+def _run_gated_chunked(K, *args):
+    K.force_gated_chunks = True
+    try:
+        return _run_gated(K, *args)
+    finally:
+        K.force_gated_chunks = False
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(3, 8, 12, 4.0, 0.0), (2, 40, 64, 12.0, 0.0), (1, 24, 40, 1.0, -9.0),
+                                   (2, 136, 33, 2.0, 0.0), (4, 128, 256, 8.0, 2.0), (2, 256, 70, 1.0, -4.0)])
+def test_learned_decays_in_chunks(dtype, shape):
+    """The chunked kernels against the recurrence's closed form: requests shorter than a chunk, a
+    chunk exactly, a chunk and one token, several chunks; cuts inside chunks; channels that decay to
+    nothing within a chunk (no exponent may overflow); records as slices of a dirty larger one; and
+    the state they leave is the state the token-by-token kernel continues from."""
+    from servelab_b200.ops import kernels as K
+    Hh, D, Dv, tau, shift = shape
+    lens = [20, 32, 33, 131]
+    T = sum(lens)
+    proj, z, bias = _gated_case(41, Hh, D, Dv, T, dtype, z_shift=shift)
+    want = _gated_want(proj, z, bias, Hh, D, Dv, lens, tau, D ** -0.5)
+    proj, z, bias = proj.to(DEV), z.to(DEV), bias.to(DEV)
+    starts = [0, 20, 52, 85]
+    rec = Hh * D * Dv
+    scale = max(1.0, float(want.abs().max()))
+    # (1) each request whole, all in one step
+    big = torch.full((4, rec + 8), 3.0, device=DEV)
+    state = big[:, 4:4 + rec]
+    state.zero_()
+    out = _run_gated_chunked(K, proj, z, bias, state, Hh, D, Dv,
+                             [[(i, a, n) for i, (a, n) in enumerate(zip(starts, lens))]], tau, D ** -0.5)
+    assert (out.double().cpu() - want).abs().max() < 3e-5 * scale
+    assert float(big[:, :4].min()) == 3.0 and float(big[:, 4 + rec:].min()) == 3.0
+    # (2) the long request cut inside chunks, the last 17 tokens one by one (the recurrent kernel)
+    state.zero_()
+    a = starts[3]
+    cuts = [(3, a, 45), (3, a + 45, 16), (3, a + 61, 53)] + [(3, a + 114 + i, 1) for i in range(17)]
+    out2 = _run_gated_chunked(K, proj, z, bias, state, Hh, D, Dv, [[cut] for cut in cuts], tau, D ** -0.5)
+    assert (out2[a:].double().cpu() - want[a:]).abs().max() < 3e-5 * scale
+    # (3) the recurrent kernel on the same rows leaves the same state
+    final = state[3].clone()
+    state.zero_()
+    _run_gated(K, proj, z, bias, state, Hh, D, Dv, [[(3, a, 131)]], tau, D ** -0.5)
+    assert (final - state[3]).abs().max() < 3e-5 * max(1.0, float(state[3].abs().max()))
+
+
+def test_learned_decays_in_chunks_keep_or_forget_a_key_from_far_back():
+    from servelab_b200.ops import kernels as K
+    Hh, D, Dv, T = 2, 16, 8, 1501
+    proj = torch.zeros(T, 2 * Hh * D + Hh * Dv)
+    proj[0, Hh * D:2 * Hh * D] = 1.0
+    proj[0, 2 * Hh * D:] = 5.0
+    proj[T - 1, :Hh * D] = 1.0
+    z = torch.full((T, Hh * D), 30.0)
+    z[:, D:] = 3.0
+    state = torch.zeros(1, Hh * D * Dv, device=DEV)
+    out = _run_gated_chunked(K, proj.to(DEV), z.to(DEV), torch.zeros(Hh * D, device=DEV), state, Hh, D, Dv,
+                             [[(0, 0, 700)], [(0, 700, 801)]], 2.0, 1.0)
     last = out[T - 1].cpu().view(Hh, Dv)
     assert (last[0] - 5.0 * D).abs().max() < 1e-2 and last[1].abs().max() < 1e-6
 
