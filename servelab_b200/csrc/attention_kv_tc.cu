@@ -179,7 +179,12 @@ __global__ void __launch_bounds__(THREADS, TMEM_COLS == 512 ? 1 : 2) attention_k
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_q,
     const int* __restrict__ ctx_len, const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
     int H, int Hkv, int ps, int box_rows, float scale_log2, int window, int* __restrict__ status, int tied,
-    const bf16* __restrict__ gate, int ldg, int maps, float* __restrict__ out32, int ldo32) {
+    const bf16* __restrict__ gate, int ldg, int maps, float* __restrict__ out32, int ldo32,
+    float cap_in, float cap_back, const float* __restrict__ sink) {
+    // cap_in > 0: a soft cap c on the scaled scores.  With s the raw score, cap_in = 2 log2(e) scale / c
+    // and cap_back = c / scale, the raw score becomes cap_back tanh(s scale / c), so that what follows
+    // (which multiplies by scale log2 e) sees the capped score; tanh(x) = 1 - 2 / (e^(2x) + 1).
+    // sink: one number a head whose exponential joins the softmax's denominator when a row is finished.
     extern __shared__ __align__(1024) unsigned char smem[];
     // All barriers come in pairs indexed by tile parity.  s_full[b]: Q.K^T of a tile is done
     // (its scores are ready and its keys may be replaced); pv_done[b]: its P.V is done (its
@@ -381,6 +386,15 @@ __global__ void __launch_bounds__(THREADS, TMEM_COLS == 512 ? 1 : 2) attention_k
             tmem_ld32(tmem + lane_base + S_COL + 64 * (j & 1), raw[0]);
             tmem_ld32(tmem + lane_base + S_COL + 64 * (j & 1) + 32, raw[1]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (cap_in > 0.f) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float t = fast_exp2(__uint_as_float(raw[h][i]) * cap_in);
+                        raw[h][i] = __float_as_uint(cap_back * (1.0f - __fdividef(2.0f, t + 1.0f)));
+                    }
+            }
             const int k0 = kbeg + j * BN;
             // raw scores stay unscaled; masked ones become -inf.  A tile that every row of
             // the block sees completely needs no mask (rows of padding compute garbage that
@@ -448,8 +462,10 @@ __global__ void __launch_bounds__(THREADS, TMEM_COLS == 512 ? 1 : 2) attention_k
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         pdl_launch_dependents();
-        float inv = l > 0.f ? 1.f / l : 0.f;
         const int tl = r / g, hg = r - tl * g;
+        if (sink != nullptr && r < nrows)
+            l += (m_ref == -INFINITY) ? 1.f : exp2f(sink[kvh * g + hg] * 1.4426950408889634f - m_ref);
+        float inv = l > 0.f ? 1.f / l : 0.f;
         if (gate != nullptr && r < nrows)
             inv *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)(q0 + tok0 + tl) * ldg + kvh * g + hg])));
         bf16* dst = out + (size_t)(q0 + tok0 + tl) * ldo + (size_t)(kvh * g + hg) * DV;
@@ -505,8 +521,10 @@ static int launch_attention_kv_tc(const bf16* q, int ldq, const bf16* kc, const 
                                   const int* block_table, int max_pages, const int* cu_q, const int* ctx_len,
                                   const int* tile_seq, const int* tile_row0, int num_tiles, int H, int Hkv, int ps,
                                   int num_pages, float scale, int window, const bf16* gate, int ldg, int maps,
-                                  float* out32, int ldo32, cudaStream_t st) {
+                                  float* out32, int ldo32, cudaStream_t st, float softcap = 0.f,
+                                  const float* sink = nullptr) {
     if (num_tiles <= 0) return 0;
+    if (softcap < 0.f || (sink != nullptr && maps != 1)) return SLB_ERR_BAD_ARG;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f) || maps < 1 ||
         maps > 64)
         return SLB_ERR_BAD_ARG;
@@ -540,7 +558,9 @@ static int launch_attention_kv_tc(const bf16* q, int ldq, const bf16* kc, const 
     if (e != cudaSuccess) return (int)e;
     return slb_launch(attention_kv_tc_kernel, dim3((unsigned)num_tiles * Hkv * maps), dim3(THREADS), smem, st, q, ldq,
                       map_k, map_v, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq, tile_row0, H, Hkv,
-                      ps, box_rows, scale * 1.4426950408889634f, window, status, tied, gate, ldg, maps, out32, ldo32);
+                      ps, box_rows, scale * 1.4426950408889634f, window, status, tied, gate, ldg, maps, out32, ldo32,
+                      softcap > 0.f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.f,
+                      softcap > 0.f ? softcap / scale : 0.f, sink);
 }
 
 extern "C" {
@@ -553,6 +573,17 @@ int slb_attention_kv_tc_bf16(const bf16* q, int ldq, const bf16* kc, const bf16*
     return launch_attention_kv_tc(q, ldq, kc, vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
                                   tile_row0, num_tiles, H, Hkv, ps, num_pages, scale, window, gate, ldg, 1, nullptr,
                                   0, st);
+}
+// The same with a soft cap on the scaled scores (`softcap` > 0: s <- softcap tanh(s / softcap)) and a
+// sink a head (`sink` [H] float32 or null) in the softmax's denominator.
+int slb_attention_kv_tc_capped_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int tied, bf16* out,
+                                    int ldo, const int* block_table, int max_pages, const int* cu_q,
+                                    const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
+                                    int H, int Hkv, int ps, int num_pages, float scale, int window, const bf16* gate,
+                                    int ldg, float softcap, const float* sink, cudaStream_t st) {
+    return launch_attention_kv_tc(q, ldq, kc, vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
+                                  tile_row0, num_tiles, H, Hkv, ps, num_pages, scale, window, gate, ldg, 1, nullptr,
+                                  0, st, softcap, sink);
 }
 // `maps` attention maps a head: q [T][H][maps][DK], k_cache [num_pages][Hkv][ps][maps * DK], one set
 // of values a kv head, float32 results per map out32 [T][H][maps][DV].
@@ -591,6 +622,11 @@ int slb_attention_kv_tc_supported(int, int, int) { return 0; }
 int slb_attention_kv_tc_bf16(const bf16*, int, const bf16*, const bf16*, int, bf16*, int, const int*, int, const int*,
                              const int*, const int*, const int*, int, int, int, int, int, float, int, const bf16*,
                              int, cudaStream_t) {
+    return SLB_ERR_BAD_ARG;
+}
+int slb_attention_kv_tc_capped_bf16(const bf16*, int, const bf16*, const bf16*, int, bf16*, int, const int*, int,
+                                    const int*, const int*, const int*, const int*, int, int, int, int, int, float,
+                                    int, const bf16*, int, float, const float*, cudaStream_t) {
     return SLB_ERR_BAD_ARG;
 }
 int slb_attention_kv_tc_maps_bf16(const bf16*, int, const bf16*, const bf16*, float*, int, const int*, int, const int*,

@@ -31,7 +31,7 @@
 #define GC_CHUNK 32
 #define GC_EV 64
 #define GC_MAX_D 256
-#define GC_SCAN_BATCH 8
+#define GC_SCAN_BATCH 16
 
 struct GatedChunkArgs {
     DecayAttnArgs a;
@@ -69,15 +69,22 @@ __global__ void __launch_bounds__(256) gated_chunk_prep_kernel(const GatedChunkA
     const T* proj = reinterpret_cast<const T*>(a.proj);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         const float b = a.gate_bias != nullptr ? a.gate_bias[h * D + d] : 0.f;
+        float zs[GC_CHUNK];                                  // (every load of the chunk before the first sum)
+#pragma unroll
+        for (int j = 0; j < GC_CHUNK; ++j)
+            zs[j] = j < n ? a.gate_z[(size_t)(t0 + j) * a.ld_gate + h * D + d] + b : 0.f;
         float run = 0.f;
-        for (int j = 0; j < n; ++j) {
-            const float z = a.gate_z[(size_t)(t0 + j) * a.ld_gate + h * D + d] + b;
-            run += (fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * a.gate_inv_tau;       // log sigmoid(z) / tau
-            Ls[j * LD + d] = run;
-            c.logs[(size_t)(t0 + j) * ((size_t)a.H * D) + h * D + d] = run;
+#pragma unroll
+        for (int j = 0; j < GC_CHUNK; ++j) {
+            if (j < n) {
+                run += (fminf(zs[j], 0.f) - log1pf(expf(-fabsf(zs[j])))) * a.gate_inv_tau;   // log sigmoid(z) / tau
+                Ls[j * LD + d] = run;
+                c.logs[(size_t)(t0 + j) * ((size_t)a.H * D) + h * D + d] = run;
+            }
         }
         c.dtot[((size_t)tile * a.H + h) * D + d] = expf(run);
     }
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < n * D; idx += blockDim.x) {
         const int j = idx / D, d = idx - j * D;
         const T* row = proj + (size_t)(t0 + j) * a.ld;
@@ -118,12 +125,14 @@ __global__ void __launch_bounds__(256) gated_chunk_local_kernel(const GatedChunk
     const T* proj = reinterpret_cast<const T*>(a.proj);
     const size_t ldl = (size_t)a.H * D;
     const float* Llast = c.logs + (size_t)(t0 + n - 1) * ldl + h * D;
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < n * D; idx += blockDim.x) {
         const int j = idx / D, d = idx - j * D;
         const T* row = proj + (size_t)(t0 + j) * a.ld;
         const float w = expf(Llast[d] - c.logs[(size_t)(t0 + j) * ldl + h * D + d]);
         kk[idx] = da_prepared(row + a.k_off + h * D, d, a.positions[t0 + j], a) * a.k_scale * w;
     }
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < n * GC_EV; idx += blockDim.x) {
         const int j = idx / GC_EV, e = e0 + (idx - j * GC_EV);
         float v = 0.f;
@@ -228,6 +237,7 @@ __global__ void __launch_bounds__(256) gated_chunk_out_kernel(const GatedChunkAr
     float* As = vs + GC_CHUNK * GC_EV;           // [GC_CHUNK][GC_CHUNK + 1]
     const T* proj = reinterpret_cast<const T*>(a.proj);
     const size_t ldl = (size_t)a.H * D;
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < GC_CHUNK * D; idx += blockDim.x) {
         const int j = idx / D, d = idx - j * D;
         float q = 0.f;
@@ -239,10 +249,21 @@ __global__ void __launch_bounds__(256) gated_chunk_out_kernel(const GatedChunkAr
         qt[j * LD + d] = q;
     }
     const float* w = c.work + ((size_t)tile * a.H + h) * (size_t)D * Dv;
-    for (int idx = threadIdx.x; idx < D * GC_EV; idx += blockDim.x) {
-        const int d = idx / GC_EV, e = e0 + (idx - d * GC_EV);
-        Sin[idx] = e < Dv ? w[(size_t)d * Dv + e] : 0.f;
+    if ((Dv & 3) == 0 && e0 + GC_EV <= Dv) {               // whole rows of the slice, 16 bytes a load
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < D * (GC_EV / 4); idx += blockDim.x) {
+            const int d = idx / (GC_EV / 4), e4 = idx - d * (GC_EV / 4);
+            *reinterpret_cast<float4*>(Sin + d * GC_EV + e4 * 4) =
+                *reinterpret_cast<const float4*>(w + (size_t)d * Dv + e0 + e4 * 4);
+        }
+    } else {
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < D * GC_EV; idx += blockDim.x) {
+            const int d = idx / GC_EV, e = e0 + (idx - d * GC_EV);
+            Sin[idx] = e < Dv ? w[(size_t)d * Dv + e] : 0.f;
+        }
     }
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < GC_CHUNK * GC_EV; idx += blockDim.x) {
         const int j = idx / GC_EV, e = e0 + (idx - j * GC_EV);
         float v = 0.f;

@@ -108,6 +108,7 @@ def check_kv_supported(key_dim: int, value_dim: int) -> None:
 
 
 use_equal_size_kernels = True
+use_kv_tc_capped = True    # a cap or a sink in steps with prompt portions: the tcgen05 kernel (off: mma.sync)
 use_kv_fast = True         # bfloat16: the tensor-core kernel (off: the plain kernel, its twin)
 KV_FAST_MAX_KEY_DIM, KV_FAST_MAX_VALUE_DIM = 320, 256
 
@@ -130,8 +131,9 @@ def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk,
     apart in ``v_cache``, which may be the key cache: the values are then a prefix of the key
     rows), causal with an optional window, head h's row times sigmoid(head_gate[t, h]) if given.
     ``softcap``: a scaled score s becomes softcap tanh(s / softcap); ``sink`` float32 [H]: a
-    number a head whose exponential joins the softmax's denominator.  The mma.sync and the plain
-    kernel take both; the tcgen05 kernels take neither, so a mixer that has one does not reach them.
+    number a head whose exponential joins the softmax's denominator.  The tcgen05 kernel for two
+    sizes, the mma.sync kernel and the plain kernel take both; the kernels for equal sizes of the
+    other models take neither, so a mixer that has one does not reach them.
     float32, or sizes the tensor-core kernel does not take: the plain kernel."""
     tied = v_cache.data_ptr() == k_cache.data_ptr() and v_row_stride == Dk
     modified = bool(softcap) or sink is not None
@@ -145,10 +147,10 @@ def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk,
         return
     if _kv_fast(Dk, Dv, q.dtype) and (tied or v_row_stride == Dv) and q.stride(0) % 8 == 0 \
             and out.stride(0) % 2 == 0:
-        if (not ctx.decode_only and not modified and out.stride(0) % 8 == 0
+        if (not ctx.decode_only and out.stride(0) % 8 == 0 and (use_kv_tc_capped or not modified)
                 and K.attention_kv_tc_takes(Dk, Dv, page_size, H // Hkv, tied)):
             K.attention_kv_tc(ctx, q, k_cache, v_cache, tied, out, table, H, Hkv, Dk, Dv, page_size, scale,
-                              window, head_gate)
+                              window, head_gate, softcap or 0.0, sink)
             return
         K.attention_kv_mma(ctx, q, k_cache, v_cache, tied, out, table, H, Hkv, Dk, Dv, page_size, scale,
                            window, head_gate, softcap or 0.0, sink)

@@ -1040,18 +1040,24 @@ def attention_kv_tc_takes(k_dim: int, v_dim: int, page_size: int, group: int, ti
 
 def attention_kv_tc(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num_heads: int,
                     num_kv_heads: int, k_dim: int, v_dim: int, page_size: int, scale: float, window: int,
-                    head_gate: Optional[torch.Tensor] = None) -> None:
+                    head_gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                    sink: Optional[torch.Tensor] = None) -> None:
     """The tcgen05 kernel (bfloat16; key and value sizes multiples of 64; steps with prompt
-    portions): 128 flattened rows a block, accumulators in tensor memory."""
+    portions): 128 flattened rows a block, accumulators in tensor memory.  ``softcap`` and ``sink``
+    as in ``attention_kv``."""
     lib = L.attention_kv(k_dim, v_dim)
     group = num_heads // num_kv_heads
     tile_seq, tile_row0, n = ctx.attention_tiles(group, lib.slb_attention_kv_tc_tile_rows(group))
-    L.check(lib.slb_attention_kv_tc_bf16(
-        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), 1 if tied else 0, out.data_ptr(),
-        out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
-        ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads,
-        page_size, k_cache.shape[0], float(scale), int(window), _p(head_gate),
-        head_gate.stride(0) if head_gate is not None else 0, _stream()), "attention_kv_tc")
+    args = (q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), 1 if tied else 0, out.data_ptr(),
+            out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
+            ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads,
+            page_size, k_cache.shape[0], float(scale), int(window), _p(head_gate),
+            head_gate.stride(0) if head_gate is not None else 0)
+    if softcap or sink is not None:
+        L.check(lib.slb_attention_kv_tc_capped_bf16(*args, float(softcap or 0.0), _p(sink), _stream()),
+                "attention_kv_tc")
+        return
+    L.check(lib.slb_attention_kv_tc_bf16(*args, _stream()), "attention_kv_tc")
 
 
 def attention_kv_tc_maps(ctx, q, k_cache, v_cache, out, block_table, num_heads: int, num_kv_heads: int,

@@ -278,6 +278,7 @@ _ATTN_KV_SIGNATURES = {
     "slb_attention_kv_tc_status": [I],
     "slb_attention_kv_tc_where": [P],
     "slb_attention_kv_tc_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P, I, P],
+    "slb_attention_kv_tc_capped_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P, I, F, P, P],
     "slb_attention_kv_tc_maps_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],
 }
 

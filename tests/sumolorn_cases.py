@@ -69,10 +69,10 @@ B = {"architecture": "Sumolorn", "vocab": 97, "width": 50, "norm": {"eps": 1e-5}
 # sizes in multiples of 64 (the tensor-core attentions of every kind), the whole model twice
 C = {"architecture": "Sumolorn", "vocab": 150, "width": 128, "norm": {"eps": 1e-5}, "logit_scale": 2.0,
      "loop": {"start": 0, "stop": 3, "times": 2},
-     "layers": [layer(attention(4, 1, 64, 64, 0.125, window=70, rot=(1e6, 32, (4.0, 1.0, 4.0, 64)), softcap=15.0),
+     "layers": [layer(attention(4, 1, 64, 64, 0.06, window=70, rot=(1e6, 32, (4.0, 1.0, 4.0, 64)), softcap=15.0),
                       dense(64, 1.2)),
-                layer(parallel((5, 4, 2, 64, 64, 0.12, 33, (3e5, 64)), (2, 64, 128, 12.0, 16)), dense(96, 3.0)),
-                layer(latent(4, 64, 64, 64, 64, 48, 1.5e5, 0.09), dense(64, 0.9))]}
+                layer(parallel((5, 4, 2, 64, 64, 0.08, 33, (3e5, 64)), (2, 64, 128, 12.0, 16)), dense(96, 3.0)),
+                layer(latent(4, 64, 64, 64, 64, 48, 1.5e5, 0.05), dense(64, 0.9))]}
 # sizes in multiples of 16 but not of 64, an empty loop, a window beyond every request
 D = {"architecture": "Sumolorn", "vocab": 320, "width": 192, "norm": {"eps": 1e-6}, "logit_scale": 0.125,
      "loop": {"start": 2, "stop": 2, "times": 4},

@@ -217,6 +217,17 @@ def test_attention_with_a_soft_cap_and_a_sink(dtype, spike, shape, decode):
         finally:
             A.force_generic = False
         assert (twin.double().cpu() - case["want"]).abs().max() < tol
+        # ... and the mma.sync kernel the twin of the tcgen05 one (sizes in multiples of 64, prompts)
+        A.use_kv_tc_capped = False
+        try:
+            A.kv_attention(ctx, case["q"], case["kc"], case["vc"], Dv, twin, ctx.block_tables[0], Hq, G, Dk, Dv,
+                           ps, 0.2, window or 0, None, cap, sink.to(DEV))
+        finally:
+            A.use_kv_tc_capped = True
+        assert (twin.double().cpu() - case["want"]).abs().max() < tol
+        if Dk % 64 == 0 and Dv % 64 == 0:
+            from servelab_b200.ops import kernels as K
+            assert K.attention_kv_tc_status(Dk, Dv) == 0 and K.attention_kv_mma_status(Dk, Dv) == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
