@@ -358,8 +358,8 @@ def _sumolorn_rooflines(size, res, peaks) -> Dict[str, object]:
     if s_dec and d_dec:
         out["decode_b8_softmax_attention_us_all_layers"] = {"sumolorn": round(s_dec, 2), "daferax": round(d_dec, 2)}
         out["decode_b8_softmax_attention_hbm_frac"] = {"sumolorn": hbm(rows, s_dec), "daferax": hbm(rows, d_dec)}
-    if sp.get("decay_attention"):
-        us = sp["decay_attention"]
+    if sp.get("decay_attention (gated chunks)") or sp.get("decay_attention"):
+        us = sp.get("decay_attention (gated chunks)") or sp["decay_attention"]
         out["sumolorn_linear_prefill_us"] = round(us, 1)
         out["sumolorn_linear_prefill_bf16_frac"] = tf(4.0 * PROMPT * lh * ld * lv, us)
     if sd.get("decay_attention"):
