@@ -17,8 +17,9 @@
 // projections are bfloat16).
 //
 // Four launches:
-//   1. per (chunk, head): L for the chunk's tokens (kept for launches 2 and 4), e^(L_last), and the
-//      masked scores A;
+//   1. per (chunk, head): L for the chunk's tokens, e^(L_last), the masked scores A, and -- kept for
+//      launches 2 and 4, so that they only copy -- the queries times e^(L_t) and the keys times
+//      e^(L_last - L_j);
 //   2. per (chunk, head, 64 value columns): the chunk's own sum  sum_j e^(L_last - L_j) k_j v_j^T
 //      into a work buffer;
 //   3. per state element: the walk over a request's chunks, S <- e^(L_last) S + sum; the work
@@ -37,7 +38,8 @@ struct GatedChunkArgs {
     DecayAttnArgs a;
     const int* tile_seq; const int* tile_row0; int num_tiles;
     float* work;        // [num_tiles][H][D][Dv]
-    float* logs;        // [tokens][H * D]
+    float* qdec;        // [tokens][H * D]: q_t[d] e^(L_t[d])
+    float* kdec;        // [tokens][H * D]: k_j[d] e^(L_last[d] - L_j[d])
     float* dtot;        // [num_tiles][H][D]
     float* scores;      // [num_tiles][H][GC_CHUNK][GC_CHUNK]
 };
@@ -67,44 +69,59 @@ __global__ void __launch_bounds__(256) gated_chunk_prep_kernel(const GatedChunkA
     float* qs = Ls + GC_CHUNK * LD;
     float* ks = qs + GC_CHUNK * LD;
     const T* proj = reinterpret_cast<const T*>(a.proj);
+    // the logarithms of the decays, every (token, channel) on a thread of its own ...
+#pragma unroll 4
+    for (int idx = threadIdx.x; idx < n * D; idx += blockDim.x) {
+        const int j = idx / D, d = idx - j * D;
+        float z = a.gate_z[(size_t)(t0 + j) * a.ld_gate + h * D + d];
+        if (a.gate_bias != nullptr) z += a.gate_bias[h * D + d];
+        Ls[j * LD + d] = (fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * a.gate_inv_tau;      // log sigmoid(z) / tau
+    }
+    __syncthreads();
+    // ... then their running sums, a channel a thread, in the order of the tokens
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        const float b = a.gate_bias != nullptr ? a.gate_bias[h * D + d] : 0.f;
-        float zs[GC_CHUNK];                                  // (every load of the chunk before the first sum)
-#pragma unroll
-        for (int j = 0; j < GC_CHUNK; ++j)
-            zs[j] = j < n ? a.gate_z[(size_t)(t0 + j) * a.ld_gate + h * D + d] + b : 0.f;
         float run = 0.f;
-#pragma unroll
-        for (int j = 0; j < GC_CHUNK; ++j) {
-            if (j < n) {
-                run += (fminf(zs[j], 0.f) - log1pf(expf(-fabsf(zs[j])))) * a.gate_inv_tau;   // log sigmoid(z) / tau
-                Ls[j * LD + d] = run;
-                c.logs[(size_t)(t0 + j) * ((size_t)a.H * D) + h * D + d] = run;
-            }
+        for (int j = 0; j < n; ++j) {
+            run += Ls[j * LD + d];
+            Ls[j * LD + d] = run;
         }
         c.dtot[((size_t)tile * a.H + h) * D + d] = expf(run);
     }
+    __syncthreads();
+    const size_t ldl = (size_t)a.H * D;
 #pragma unroll 4
     for (int idx = threadIdx.x; idx < n * D; idx += blockDim.x) {
         const int j = idx / D, d = idx - j * D;
         const T* row = proj + (size_t)(t0 + j) * a.ld;
         const int pos = a.positions[t0 + j];
-        qs[j * LD + d] = da_prepared(row + a.q_off + h * D, d, pos, a) * a.q_scale;
-        ks[j * LD + d] = da_prepared(row + a.k_off + h * D, d, pos, a) * a.k_scale;
+        const float qv = da_prepared(row + a.q_off + h * D, d, pos, a) * a.q_scale;
+        const float kv = da_prepared(row + a.k_off + h * D, d, pos, a) * a.k_scale;
+        const float L = Ls[j * LD + d];
+        qs[j * LD + d] = qv;
+        ks[j * LD + d] = kv;
+        c.qdec[(size_t)(t0 + j) * ldl + h * D + d] = qv * expf(L);
+        c.kdec[(size_t)(t0 + j) * ldl + h * D + d] = kv * expf(Ls[(n - 1) * LD + d] - L);
     }
     __syncthreads();
     float* A = c.scores + ((size_t)tile * a.H + h) * (GC_CHUNK * GC_CHUNK);
-    for (int e = threadIdx.x; e < GC_CHUNK * GC_CHUNK; e += blockDim.x) {
-        const int t = e / GC_CHUNK, j = e - t * GC_CHUNK;
+    for (int e = threadIdx.x; e < GC_CHUNK * GC_CHUNK; e += blockDim.x) A[e] = 0.f;      // (above the diagonal)
+    // The pairs (t, j <= t) of the chunk, numbered along the rows of the triangle so that every
+    // thread gets as many: pair e sits in row t with t (t + 1) / 2 <= e.
+    const int pairs = n * (n + 1) / 2;
+    for (int e = threadIdx.x; e < pairs; e += blockDim.x) {
+        int t = (int)((sqrtf(8.0f * (float)e + 1.0f) - 1.0f) * 0.5f);
+        while (t * (t + 1) / 2 > e) --t;                   // (the root's rounding)
+        while ((t + 1) * (t + 2) / 2 <= e) ++t;
+        const int j = e - t * (t + 1) / 2;
+        const float* qt = qs + t * LD;
+        const float* kj = ks + j * LD;
+        const float* Lt = Ls + t * LD;
+        const float* Lj = Ls + j * LD;
         float sum = 0.f;
-        if (t < n && j <= t) {
-            const float* qt = qs + t * LD;
-            const float* kj = ks + j * LD;
-            const float* Lt = Ls + t * LD;
-            const float* Lj = Ls + j * LD;
-            for (int d = 0; d < D; ++d) sum = fmaf(qt[d] * kj[d], expf(Lt[d] - Lj[d]), sum);
-        }
-        A[e] = sum;
+        // (the exponent is <= 0; the one-instruction 2^x is exact to 2 ulp there, and its argument's
+        // rounding weighs on terms that are small by the same factor)
+        for (int d = 0; d < D; ++d) sum = fmaf(qt[d] * kj[d], __expf(Lt[d] - Lj[d]), sum);
+        A[t * GC_CHUNK + j] = sum;
     }
 }
 
@@ -124,13 +141,19 @@ __global__ void __launch_bounds__(256) gated_chunk_local_kernel(const GatedChunk
     float* vs = kk + GC_CHUNK * D;               // [GC_CHUNK][GC_EV]
     const T* proj = reinterpret_cast<const T*>(a.proj);
     const size_t ldl = (size_t)a.H * D;
-    const float* Llast = c.logs + (size_t)(t0 + n - 1) * ldl + h * D;
+    const float* kd = c.kdec + (size_t)t0 * ldl + h * D;
+    if ((D & 3) == 0) {                                   // (rows of launch 1's decayed keys, 16 bytes a load)
 #pragma unroll 4
-    for (int idx = threadIdx.x; idx < n * D; idx += blockDim.x) {
-        const int j = idx / D, d = idx - j * D;
-        const T* row = proj + (size_t)(t0 + j) * a.ld;
-        const float w = expf(Llast[d] - c.logs[(size_t)(t0 + j) * ldl + h * D + d]);
-        kk[idx] = da_prepared(row + a.k_off + h * D, d, a.positions[t0 + j], a) * a.k_scale * w;
+        for (int idx = threadIdx.x; idx < n * (D / 4); idx += blockDim.x) {
+            const int j = idx / (D / 4), d4 = idx - j * (D / 4);
+            *reinterpret_cast<float4*>(kk + j * D + d4 * 4) = *reinterpret_cast<const float4*>(kd + j * ldl + d4 * 4);
+        }
+    } else {
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < n * D; idx += blockDim.x) {
+            const int j = idx / D, d = idx - j * D;
+            kk[idx] = kd[j * ldl + d];
+        }
     }
 #pragma unroll 4
     for (int idx = threadIdx.x; idx < n * GC_EV; idx += blockDim.x) {
@@ -230,23 +253,27 @@ __global__ void __launch_bounds__(256) gated_chunk_out_kernel(const GatedChunkAr
     const int tile = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * GC_EV;
     int t0, n;
     if (!gc_tile(c, tile, t0, n)) return;
-    const int D = a.D, Dv = a.Dv, LD = D + 1;
-    float* qt = gc_smem;                         // [GC_CHUNK][D + 1]: q_t[d] e^(L_t[d]); zero rows beyond n
+    const int D = a.D, Dv = a.Dv, LD = (D + 3) & ~3;
+    float* qt = gc_smem;                         // [GC_CHUNK][LD]: q_t[d] e^(L_t[d]); zero rows beyond n
     float* Sin = qt + GC_CHUNK * LD;             // [D][GC_EV]: the entering state's slice
     float* vs = Sin + (size_t)D * GC_EV;         // [GC_CHUNK][GC_EV]
     float* As = vs + GC_CHUNK * GC_EV;           // [GC_CHUNK][GC_CHUNK + 1]
     const T* proj = reinterpret_cast<const T*>(a.proj);
     const size_t ldl = (size_t)a.H * D;
+    const float* qd = c.qdec + (size_t)t0 * ldl + h * D;
+    if ((D & 3) == 0) {                                   // (rows of launch 1's decayed queries, 16 bytes a load)
 #pragma unroll 4
-    for (int idx = threadIdx.x; idx < GC_CHUNK * D; idx += blockDim.x) {
-        const int j = idx / D, d = idx - j * D;
-        float q = 0.f;
-        if (j < n) {
-            const T* row = proj + (size_t)(t0 + j) * a.ld;
-            q = da_prepared(row + a.q_off + h * D, d, a.positions[t0 + j], a) * a.q_scale *
-                expf(c.logs[(size_t)(t0 + j) * ldl + h * D + d]);
+        for (int idx = threadIdx.x; idx < GC_CHUNK * (D / 4); idx += blockDim.x) {
+            const int j = idx / (D / 4), d4 = idx - j * (D / 4);
+            *reinterpret_cast<float4*>(qt + j * LD + d4 * 4) =
+                j < n ? *reinterpret_cast<const float4*>(qd + j * ldl + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        qt[j * LD + d] = q;
+    } else {
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < GC_CHUNK * D; idx += blockDim.x) {
+            const int j = idx / D, d = idx - j * D;
+            qt[j * LD + d] = j < n ? qd[j * ldl + d] : 0.f;
+        }
     }
     const float* w = c.work + ((size_t)tile * a.H + h) * (size_t)D * Dv;
     if ((Dv & 3) == 0 && e0 + GC_EV <= Dv) {               // whole rows of the slice, 16 bytes a load
@@ -282,24 +309,34 @@ __global__ void __launch_bounds__(256) gated_chunk_out_kernel(const GatedChunkAr
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     const float* q0 = qt + ty * LD;
     const float* q1 = qt + (ty + 16) * LD;
-    for (int d = 0; d < D; ++d) {
+#define GC_ROW(a0, a1, s4)                                                                  \
+    acc[0][0] = fmaf(a0, s4.x, acc[0][0]); acc[0][1] = fmaf(a0, s4.y, acc[0][1]);           \
+    acc[0][2] = fmaf(a0, s4.z, acc[0][2]); acc[0][3] = fmaf(a0, s4.w, acc[0][3]);           \
+    acc[1][0] = fmaf(a1, s4.x, acc[1][0]); acc[1][1] = fmaf(a1, s4.y, acc[1][1]);           \
+    acc[1][2] = fmaf(a1, s4.z, acc[1][2]); acc[1][3] = fmaf(a1, s4.w, acc[1][3]);
+    int d = 0;
+    for (; d + 4 <= D; d += 4) {                           // (four state rows a step: the queries 16 bytes a load)
+        const float4 qa = *reinterpret_cast<const float4*>(q0 + d);
+        const float4 qb = *reinterpret_cast<const float4*>(q1 + d);
+        const float4 s0 = *reinterpret_cast<const float4*>(Sin + d * GC_EV + ex * 4);
+        const float4 s1 = *reinterpret_cast<const float4*>(Sin + (d + 1) * GC_EV + ex * 4);
+        const float4 s2 = *reinterpret_cast<const float4*>(Sin + (d + 2) * GC_EV + ex * 4);
+        const float4 s3 = *reinterpret_cast<const float4*>(Sin + (d + 3) * GC_EV + ex * 4);
+        GC_ROW(qa.x, qb.x, s0) GC_ROW(qa.y, qb.y, s1) GC_ROW(qa.z, qb.z, s2) GC_ROW(qa.w, qb.w, s3)
+    }
+    for (; d < D; ++d) {
         const float4 s4 = *reinterpret_cast<const float4*>(Sin + d * GC_EV + ex * 4);
         const float a0 = q0[d], a1 = q1[d];
-        acc[0][0] = fmaf(a0, s4.x, acc[0][0]); acc[0][1] = fmaf(a0, s4.y, acc[0][1]);
-        acc[0][2] = fmaf(a0, s4.z, acc[0][2]); acc[0][3] = fmaf(a0, s4.w, acc[0][3]);
-        acc[1][0] = fmaf(a1, s4.x, acc[1][0]); acc[1][1] = fmaf(a1, s4.y, acc[1][1]);
-        acc[1][2] = fmaf(a1, s4.z, acc[1][2]); acc[1][3] = fmaf(a1, s4.w, acc[1][3]);
+        GC_ROW(a0, a1, s4)
     }
     const float* A0 = As + ty * (GC_CHUNK + 1);
     const float* A1 = As + (ty + 16) * (GC_CHUNK + 1);
     for (int j = 0; j < n; ++j) {
         const float4 v4 = *reinterpret_cast<const float4*>(vs + j * GC_EV + ex * 4);
         const float a0 = A0[j], a1 = A1[j];
-        acc[0][0] = fmaf(a0, v4.x, acc[0][0]); acc[0][1] = fmaf(a0, v4.y, acc[0][1]);
-        acc[0][2] = fmaf(a0, v4.z, acc[0][2]); acc[0][3] = fmaf(a0, v4.w, acc[0][3]);
-        acc[1][0] = fmaf(a1, v4.x, acc[1][0]); acc[1][1] = fmaf(a1, v4.y, acc[1][1]);
-        acc[1][2] = fmaf(a1, v4.z, acc[1][2]); acc[1][3] = fmaf(a1, v4.w, acc[1][3]);
+        GC_ROW(a0, a1, v4)
     }
+#undef GC_ROW
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int t = ty + 16 * r;
@@ -322,7 +359,7 @@ static int launch_gated_chunk(const GatedChunkArgs* c_in, int num_seqs, cudaStre
     if (a.H <= 0 || a.D <= 0 || a.Dv <= 0 || a.num_slots <= 0 || (a.rot_dims & 1) || a.rot_dims < 0 ||
         a.rot_dims > a.D || (a.rot_dims > 0 && a.freq == nullptr) || a.act < 0 || a.act > 1 ||
         a.gate_z == nullptr || a.ld_gate < a.H * a.D || !(a.gate_inv_tau > 0.f) ||
-        a.state_stride < (long long)a.H * a.D * a.Dv || c.work == nullptr || c.logs == nullptr ||
+        a.state_stride < (long long)a.H * a.D * a.Dv || c.work == nullptr || c.qdec == nullptr || c.kdec == nullptr ||
         c.dtot == nullptr || c.scores == nullptr || c.tile_seq == nullptr || c.tile_row0 == nullptr)
         return SLB_ERR_BAD_ARG;
     if (a.D > GC_MAX_D || a.H > 65535 || num_seqs > 65535) return SLB_ERR_TOO_LARGE;
@@ -331,7 +368,7 @@ static int launch_gated_chunk(const GatedChunkArgs* c_in, int num_seqs, cudaStre
     if (vz > 65535 || ez > 65535) return SLB_ERR_TOO_LARGE;
     const size_t smem1 = (size_t)3 * GC_CHUNK * (a.D + 1) * sizeof(float);
     const size_t smem2 = ((size_t)GC_CHUNK * a.D + GC_CHUNK * GC_EV) * sizeof(float);
-    const size_t smem4 = ((size_t)GC_CHUNK * (a.D + 1) + (size_t)a.D * GC_EV + GC_CHUNK * GC_EV +
+    const size_t smem4 = ((size_t)GC_CHUNK * ((a.D + 3) & ~3) + (size_t)a.D * GC_EV + GC_CHUNK * GC_EV +
                           GC_CHUNK * (GC_CHUNK + 1)) * sizeof(float);
     constexpr size_t MAX1 = (size_t)3 * GC_CHUNK * (GC_MAX_D + 1) * sizeof(float);
     constexpr size_t MAX4 = ((size_t)GC_CHUNK * (GC_MAX_D + 1) + (size_t)GC_MAX_D * GC_EV + GC_CHUNK * GC_EV +

@@ -1319,8 +1319,8 @@ class _DecayChunkArgs(_ct.Structure):
 
 class _GatedChunkArgs(_ct.Structure):
     _fields_ = [("a", _DecayAttnArgs), ("tile_seq", _ct.c_void_p), ("tile_row0", _ct.c_void_p),
-                ("num_tiles", _ct.c_int), ("work", _ct.c_void_p), ("logs", _ct.c_void_p), ("dtot", _ct.c_void_p),
-                ("scores", _ct.c_void_p)]
+                ("num_tiles", _ct.c_int), ("work", _ct.c_void_p), ("qdec", _ct.c_void_p), ("kdec", _ct.c_void_p),
+                ("dtot", _ct.c_void_p), ("scores", _ct.c_void_p)]
 
 
 # Learned decays: steps that bring portions of prompts in bfloat16 take the chunked kernels (float32
@@ -1380,10 +1380,11 @@ def decay_attention(proj: torch.Tensor, ctx, state: torch.Tensor, decay: Optiona
         c.tile_seq, c.tile_row0, c.num_tiles = tile_seq.data_ptr(), tile_row0.data_ptr(), n
         dev = proj.device
         work = torch.empty((max(n, 1), num_heads, head_dim, value_dim), dtype=_F32, device=dev)
-        logs = torch.empty((proj.shape[0], num_heads * head_dim), dtype=_F32, device=dev)
+        qk_dec = torch.empty((2, proj.shape[0], num_heads * head_dim), dtype=_F32, device=dev)
         dtot = torch.empty((max(n, 1), num_heads, head_dim), dtype=_F32, device=dev)
         scores = torch.empty((max(n, 1), num_heads, chunk, chunk), dtype=_F32, device=dev)
-        c.work, c.logs, c.dtot, c.scores = work.data_ptr(), logs.data_ptr(), dtot.data_ptr(), scores.data_ptr()
+        c.work, c.dtot, c.scores = work.data_ptr(), dtot.data_ptr(), scores.data_ptr()
+        c.qdec, c.kdec = qk_dec[0].data_ptr(), qk_dec[1].data_ptr()
         fn = getattr(L.core(), "slb_decay_gated_chunk_" + _suffix(proj.dtype))
         L.check(fn(_ct.byref(c), ctx.num_seqs, _stream()), "decay_attention (gated chunks)")
         global launch_count
