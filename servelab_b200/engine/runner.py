@@ -18,7 +18,7 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, state_part
 from ..cache.storage import CacheStorage, pages_from_memory, plan_groups
 from ..config.engine import CacheConfig
 from ..config.registry import load_config
@@ -82,6 +82,13 @@ class ModelRunner:
         self._graph_safe = all(
             getattr(b, "graph_safe", False)
             for b in list(self.model.blocks) + [self.model.embedding_position, self.model.final_norm])
+        # A model whose mixers keep per-request state replays padded graphs of steps with portions
+        # only if every such mixer says that a padded step is safe for it (``padded_steps_safe``:
+        # requests without tokens and tokens that belong to no request leave every record alone).
+        self._padded_state_safe = all(
+            getattr(getattr(b, "mixer", None), "padded_steps_safe", False)
+            for run, b in ((r, self.model.blocks[r.layer]) for r in self.spec.run_order)
+            if run.cache_of is None and state_part(b.cache_request(b.spec)) is not None)
         self.graph_replays = 0
         # Steps with prompt portions replay graphs too, captured for padded sizes (tokens,
         # requests, wanted rows rounded up; ``StepContext.pack(pad=...)``): a layer costs the
@@ -155,7 +162,8 @@ class ModelRunner:
             return self._step_graph(entries, token_ids_from)
         if token_ids_from is not None:
             raise ValueError("token ids from the device need a step that replays a graph")
-        if self.cuda_graphs and self.portion_graphs and self._graph_safe and not self.storage.state_layers:
+        if (self.cuda_graphs and self.portion_graphs and self._graph_safe
+                and (not self.storage.state_layers or self._padded_state_safe)):
             pad = self._portion_pad(entries)
             if pad is not None:
                 hit = self._portion_graphs.get(pad)
@@ -193,7 +201,11 @@ class ModelRunner:
         hit = self._portion_graphs.pop(pad, None)
         if hit is None:
             ctx = StepContext.pack(entries, self.num_groups, self.device, min_table_width=width, pad=pad)
+            # (the warm-up runs the step and the first replay runs it again: keys land in the same
+            # slots twice, a mixer's own state is put back in between)
+            saved = self.storage.snapshot_state(ctx.state_slot_ids)
             self.model.forward(ctx, self.storage.layer_caches)        # builds libraries, warms caches
+            self.storage.restore_state(ctx.state_slot_ids, saved)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:

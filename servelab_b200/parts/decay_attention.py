@@ -42,6 +42,8 @@ class DecayAttention(Mixer):
         if min(s.num_heads, s.head_dim, s.value_dim) <= 0:
             raise ValueError("decay_attention: heads, head_dim and value_dim must be positive")
         self.gated = s.decay_gate_rank is not None
+        # (the kernels for learned decays skip requests without tokens and tiles of padding)
+        self.padded_steps_safe = self.gated
         if self.gated and (s.decay or not s.decay_gate_tau > 0):
             raise ValueError("decay_attention: learned decays take no fixed ``decay`` and a positive tau")
         if not self.gated and len(s.decay) != s.num_heads:

@@ -49,6 +49,7 @@ def pad_rows(w: torch.Tensor, multiple: int = 8) -> torch.Tensor:
 @register_mixer("normed_attention")
 class NormedAttention(Mixer):
     graph_safe = True
+    padded_steps_safe = True      # the convolution's record is written per request with tokens only
 
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)

@@ -46,6 +46,7 @@ class ParallelMixers(Mixer):
                 raise ValueError(f"parallel_mixers: the mixer {branch.spec.kind!r} cannot return float32 results")
             branch.out_dtype = torch.float32
         self.graph_safe = all(getattr(b, "graph_safe", False) for b in (self.left, self.right))
+        self.padded_steps_safe = all(getattr(b, "padded_steps_safe", False) for b in (self.left, self.right))
         self.sizes = _record_sizes(spec)
 
     @classmethod

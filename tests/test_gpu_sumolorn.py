@@ -610,6 +610,26 @@ def test_single_token_steps_through_replayed_graphs(model, dtype):
     _compare(model, dtype, graphs)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_with_portions_through_graphs_captured_for_padded_sizes(model, dtype):
+    """Steps with prompt portions replay graphs captured for padded sizes although the model keeps
+    per-request state: the padding (requests without tokens, tokens of no request) must leave every
+    record alone, and the warm-up run before a capture must not advance a state twice."""
+    from servelab_b200.replay import TraceSession
+    steps = H.trace_mixed(model["requests"], seed=4)
+    eager, _ = _replay(model, dtype, steps)
+    sess = TraceSession(model["folder"], dtype, H.peak_tokens(steps), page_size=model["page"], max_live=4,
+                        poison_cache=True, cuda_graphs=True)
+    assert sess.runner._padded_state_safe
+    sess.runner.portion_graph_after = 1
+    got = H.collect(steps, H.run_session(sess, steps), model["cfg"]["vocab"])
+    assert sess.runner.portion_graph_replays > 0
+    for rid in eager:
+        for pos in eager[rid]:
+            assert np.abs(got[rid][pos] - eager[rid][pos]).max() <= (2e-6 if dtype == "float32" else 2e-1), (rid, pos)
+    _compare(model, dtype, got)
+
+
 def test_the_trace_runner_as_a_program(model, tmp_path):
     import json
     import os
